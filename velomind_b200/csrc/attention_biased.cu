@@ -78,7 +78,7 @@ __global__ void attn_biased_kernel(const T* __restrict__ q, int q_row_stride, co
                                    const int* __restrict__ block_table, int max_blocks, const int* __restrict__ positions,
                                    const int* __restrict__ seq_of_token, const float* __restrict__ rel, const int* __restrict__ bucket_of, int far,
                                    T* __restrict__ out, int n_tokens, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first,
-                                   int n_pages, int* __restrict__ err) {
+                                   int n_pages, const float* __restrict__ sink, int v_stride, int* __restrict__ err) {
     extern __shared__ float qs_all[];                       // ATT_WARPS x Dk
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long w = (long long)blockIdx.x * ATT_WARPS + warp;
@@ -129,7 +129,7 @@ __global__ void attn_biased_kernel(const T* __restrict__ q, int q_row_stride, co
         for (int jj = 0; jj < cnt; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             if (pj == 0.f) continue;                       // (the same for every lane)
-            const T* vrow = vpages + (tok0 + jj) * Dv;
+            const T* vrow = vpages + (tok0 + jj) * v_stride;
 #pragma unroll
             for (int i = 0; i < EPL; ++i) {
                 const int d = lane + 32 * i;
@@ -138,7 +138,13 @@ __global__ void attn_biased_kernel(const T* __restrict__ q, int q_row_stride, co
         }
         m = m_new;
     }
-    const float inv = 1.0f / l;
+    float keep = 1.0f;
+    if (sink) {                                            // one more term of the denominator: exp(sink), with no key and no value
+        const float sk = sink[h], m_all = fmaxf(m, sk);
+        keep = expf(m - m_all);
+        l = l * keep + expf(sk - m_all);
+    }
+    const float inv = keep / l;
     T* orow = out + ((size_t)t * H + h) * Dv;
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
@@ -150,7 +156,8 @@ __global__ void attn_biased_kernel(const T* __restrict__ q, int q_row_stride, co
 template <typename T>
 int launch_biased(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table, int max_blocks,
                   const int* positions, const int* seq_of_token, const float* rel, const int* bucket_of, int far, void* out, int n_tokens, int H,
-                  int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages, int* err, cudaStream_t stream) {
+                  int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages, const float* sink, int v_stride, int* err,
+                  cudaStream_t stream) {
     const long long warps = (long long)n_tokens * H;
     const int blocks = (int)((warps + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * Dk * sizeof(float);
@@ -160,7 +167,7 @@ int launch_biased(const void* q, int q_row_stride, const void* kpages, const voi
         attn_biased_kernel<T, E><<<blocks, ATT_WARPS * 32, smem, stream>>>((const T*)q, q_row_stride, (const T*)kpages, (const T*)vpages, \
                                                                            block_table, max_blocks, positions, seq_of_token, rel,       \
                                                                            bucket_of, far, (T*)out, n_tokens, H, Hkv, Dk, Dv, scale,     \
-                                                                           window, keep_first, n_pages, err);                            \
+                                                                           window, keep_first, n_pages, sink, v_stride, err);            \
         break;
     switch (epl) {
         VM_ATT_CASE(1) VM_ATT_CASE(2) VM_ATT_CASE(3) VM_ATT_CASE(4) VM_ATT_CASE(5) VM_ATT_CASE(6) VM_ATT_CASE(7) VM_ATT_CASE(8)
@@ -199,14 +206,27 @@ VM_API int vm_attention_biased_generic(const void* q, int q_row_stride, const vo
                                        const int* positions, const int* seq_of_token, const float* rel, const int* bucket_of, int far, void* out,
                                        int n_tokens, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages,
                                        int act_dtype, int* err, cudaStream_t stream) {
+    return vm_attention_sink_generic(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, seq_of_token, rel, bucket_of, far, nullptr, 0, out,
+                                     n_tokens, H, Hkv, Dk, Dv, scale, window, keep_first, n_pages, act_dtype, err, stream);
+}
+
+// The same with a sink and values that may lie inside the key rows.  sink float32 [H] (null: none): exp(sink[h]) is one more term
+// of head h's softmax denominator, without a key or a value, not scaled.  v_row_stride: elements from one token's value row to the
+// next in `vpages` (0: Dv); with vpages == kpages and v_row_stride == Dk a token's value is the first Dv values of its key row.
+VM_API int vm_attention_sink_generic(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table, int max_blocks,
+                                     const int* positions, const int* seq_of_token, const float* rel, const int* bucket_of, int far, const float* sink,
+                                     int v_row_stride, void* out, int n_tokens, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first,
+                                     int n_pages, int act_dtype, int* err, cudaStream_t stream) {
+    const int v_stride = v_row_stride > 0 ? v_row_stride : Dv;
+    if (v_stride < Dv) return VM_ERR_BAD_ARG;
     if (n_tokens <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || Dk <= 0 || Dk > 1024 || Dv <= 0 || Dv > 256 || window < 0 || keep_first < 0) return VM_ERR_UNSUPPORTED;
     if ((rel != nullptr) != (bucket_of != nullptr) || (rel && far < 0)) return VM_ERR_BAD_ARG;
     if (act_dtype == VM_F32)
         return launch_biased<float>(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, seq_of_token, rel, bucket_of, far, out, n_tokens, H,
-                                    Hkv, Dk, Dv, scale, window, keep_first, n_pages, err, stream);
+                                    Hkv, Dk, Dv, scale, window, keep_first, n_pages, sink, v_stride, err, stream);
     if (act_dtype == VM_BF16)
         return launch_biased<__nv_bfloat16>(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, seq_of_token, rel, bucket_of, far, out,
-                                            n_tokens, H, Hkv, Dk, Dv, scale, window, keep_first, n_pages, err, stream);
+                                            n_tokens, H, Hkv, Dk, Dv, scale, window, keep_first, n_pages, sink, v_stride, err, stream);
     return VM_ERR_UNSUPPORTED;
 }

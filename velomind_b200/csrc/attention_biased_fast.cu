@@ -32,21 +32,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
-template <int DK, int DV>
+// VK: a token's value is the first DV values of its key row (one pool, one tile in shared memory: nothing else is fetched for the values)
+template <int DK, int DV, bool VK>
 __global__ void __launch_bounds__(128)
 attn_biased_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride, const __nv_bfloat16* __restrict__ kpages,
                            const __nv_bfloat16* __restrict__ vpages, const int* __restrict__ block_table, int max_blocks,
                            const int* __restrict__ positions, const int* __restrict__ cu_tokens, int B, const float* __restrict__ rel,
                            const int* __restrict__ bucket_of, int far, int rel_rows, __nv_bfloat16* __restrict__ out, int H, int Hkv,
-                           float scale_log2, int window, int keep_first, int n_pages, int* __restrict__ err) {
-    constexpr int KP = DK + 8, VP = DV + 8;     // padded rows: an odd number of 16-byte units -> no ldmatrix conflicts
+                           float scale_log2, int window, int keep_first, int n_pages, const float* __restrict__ sink, int* __restrict__ err) {
+    constexpr int KP = DK + 8, VP = VK ? KP : DV + 8;     // padded rows: an odd number of 16-byte units -> no ldmatrix conflicts
     constexpr int KCH = DK / 8, VCH = DV / 8;   // 16-byte chunks per row
     constexpr float LOG2E = 1.4426950408889634f;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [BM][KP]
     __nv_bfloat16* sK = sQ + BM * KP;                                    // [2][BN][KP]
     __nv_bfloat16* sV = sK + 2 * BN * KP;                                // [2][BN][VP]
-    float* sBias = reinterpret_cast<float*>(sV + 2 * BN * VP);           // direct: [far + 1] by distance; else [rel_rows] by table row
+    float* sBias = reinterpret_cast<float*>(VK ? sV : sV + 2 * BN * VP);  // direct: [far + 1] by distance; else [rel_rows] by table row
     constexpr int THREADS = 128;
     const bool biased = rel != nullptr;
     const bool direct = biased && far + 1 <= DIRECT_TABLE_MAX;
@@ -94,10 +95,11 @@ attn_biased_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride
             const int r = c / KCH, ch = c - r * KCH;
             cp_async16_zfill(ks + r * KP + ch * 8, kg + r * DK + ch * 8, ok);
         }
-        for (int c = tid; c < BN * VCH; c += THREADS) {
-            const int r = c / VCH, ch = c - r * VCH;
-            cp_async16_zfill(vs + r * VP + ch * 8, vg + r * DV + ch * 8, ok);
-        }
+        if (!VK)
+            for (int c = tid; c < BN * VCH; c += THREADS) {
+                const int r = c / VCH, ch = c - r * VCH;
+                cp_async16_zfill(vs + r * VP + ch * 8, vg + r * DV + ch * 8, ok);
+            }
     };
     load_kv(0, 0);
     vm_cp_async_commit();
@@ -134,7 +136,7 @@ attn_biased_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride
         const bool in_reach = key0 <= warp_max_pos && (window <= 0 || key0 + BN - 1 >= warp_min_pos - window + 1 || key0 < keep_first);
         if (in_reach && warp * 16 < n_rows) {
             const __nv_bfloat16* ks = sK + (size_t)buf * BN * KP;
-            const __nv_bfloat16* vs = sV + (size_t)buf * BN * VP;
+            const __nv_bfloat16* vs = VK ? ks : sV + (size_t)buf * BN * VP;
             float s[BN / 8][4];
 #pragma unroll
             for (int nb = 0; nb < BN / 8; ++nb) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
@@ -209,7 +211,14 @@ attn_biased_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride
 
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
-    const float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+    float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+    if (sink) {                                            // exp(sink) joins the denominator (scores here are in base-2 units)
+        const float sk = sink[h] * LOG2E;
+        const float top_a = fmaxf(m_a, sk), top_b = fmaxf(m_b, sk);
+        const float keep_a = fast_exp2(m_a - top_a), keep_b = fast_exp2(m_b - top_b);
+        inv_a = keep_a / (l_a * keep_a + fast_exp2(sk - top_a));
+        inv_b = keep_b / (l_b * keep_b + fast_exp2(sk - top_b));
+    }
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i) {
         const int d = i * 8 + 2 * t4;
@@ -220,24 +229,24 @@ attn_biased_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride
     }
 }
 
-template <int DK, int DV>
+template <int DK, int DV, bool VK>
 int launch_biased_prefill(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table, int max_blocks,
                           const int* positions, const int* cu_tokens, int B, int n_tiles, const float* rel, const int* bucket_of, int far,
-                          int rel_rows, void* out, int H, int Hkv, float scale, int window, int keep_first, int n_pages, int* err,
+                          int rel_rows, void* out, int H, int Hkv, float scale, int window, int keep_first, int n_pages, const float* sink, int* err,
                           cudaStream_t stream) {
     const int table = rel ? (far + 1 <= DIRECT_TABLE_MAX ? far + 1 : rel_rows) : 0;
-    const size_t smem = (size_t)(BM + 2 * BN) * (DK + 8) * sizeof(__nv_bfloat16) + (size_t)2 * BN * (DV + 8) * sizeof(__nv_bfloat16) +
+    const size_t smem = (size_t)(BM + 2 * BN) * (DK + 8) * sizeof(__nv_bfloat16) + (VK ? 0 : (size_t)2 * BN * (DV + 8) * sizeof(__nv_bfloat16)) +
                         (size_t)table * sizeof(float);
     if (smem > 200 * 1024) return VM_ERR_UNSUPPORTED;
     static size_t raised = 48 * 1024;                       // per instantiation
     if (smem > raised) {
-        cudaError_t e = cudaFuncSetAttribute(attn_biased_prefill_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_biased_prefill_kernel<DK, DV, VK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         raised = smem;
     }
-    attn_biased_prefill_kernel<DK, DV><<<dim3(n_tiles, H), 128, smem, stream>>>(
+    attn_biased_prefill_kernel<DK, DV, VK><<<dim3(n_tiles, H), 128, smem, stream>>>(
         (const __nv_bfloat16*)q, q_row_stride, (const __nv_bfloat16*)kpages, (const __nv_bfloat16*)vpages, block_table, max_blocks, positions,
-        cu_tokens, B, rel, bucket_of, far, rel_rows, (__nv_bfloat16*)out, H, Hkv, scale * 1.4426950408889634f, window, keep_first, n_pages, err);
+        cu_tokens, B, rel, bucket_of, far, rel_rows, (__nv_bfloat16*)out, H, Hkv, scale * 1.4426950408889634f, window, keep_first, n_pages, sink, err);
     return vm_launch_status();
 }
 
@@ -251,7 +260,7 @@ attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
                           const __nv_bfloat16* __restrict__ vpages, const int* __restrict__ block_table, int max_blocks,
                           const int* __restrict__ positions, const float* __restrict__ rel, const int* __restrict__ bucket_of, int far,
                           __nv_bfloat16* __restrict__ out, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages,
-                          int* __restrict__ err) {
+                          const float* __restrict__ sink, int v_stride, int* __restrict__ err) {
     extern __shared__ __align__(16) float dsm[];            // [Dk] the query; then per warp: m, l, acc[Dv]
     float* qs = dsm;
     float* part = dsm + ((Dk + 3) & ~3);
@@ -318,7 +327,7 @@ attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
 #pragma unroll 8
         for (int jj = 0; jj < cnt; ++jj) {                 // (no branch inside: the rows' loads overlap; a key that is not seen has p = 0)
             const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const __nv_bfloat16* vrow = vpages + (tok0 + jj) * Dv;
+            const __nv_bfloat16* vrow = vpages + (tok0 + jj) * v_stride;
 #pragma unroll
             for (int i = 0; i < VPL; ++i) {
                 const int d = 2 * lane + 64 * i;
@@ -363,7 +372,11 @@ attn_biased_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stride,
             if (d < Dv) res[i] = fmaf(pw[2 + d], f, res[i]);
         }
     }
-    const float inv = 1.0f / L;
+    float inv = 1.0f / L;
+    if (sink) {                                            // exp(sink): one more term of the denominator, without a value
+        const float sk = sink[h], top = fmaxf(M, sk), keep = expf(M - top);
+        inv = keep / (L * keep + expf(sk - top));
+    }
     __nv_bfloat16* orow = out + ((size_t)seq * H + h) * Dv;
 #pragma unroll
     for (int i = 0; i < 2 * VPL; ++i) {
@@ -379,23 +392,46 @@ VM_API int vm_attention_biased_prefill_fits(int Dk, int Dv) {
     return (Dk == 32 || Dk == 64 || Dk == 96 || Dk == 128) && (Dv == 16 || Dv == 32 || Dv == 64 || Dv == 128) ? 1 : 0;
 }
 
+// 1 if vm_attention_sink_prefill_bf16 takes these sizes; values_in_keys: a token's value is the first Dv values of its key row
+VM_API int vm_attention_sink_prefill_fits(int Dk, int Dv, int values_in_keys) {
+    if (!values_in_keys) return vm_attention_biased_prefill_fits(Dk, Dv);
+    const int extra = Dk - Dv;
+    return (Dv == 16 || Dv == 32 || Dv == 64 || Dv == 128) && (extra == 16 || extra == 32 || extra == 64) ? 1 : 0;
+}
+
 // n_tiles = sum over the step's sequences of ceil(new tokens / 64), computed by the host.  rel float32 [rel_rows, H] with bucket_of
 // int32 [far + 1], or both null.  q rows of stride q_row_stride (a multiple of 8), out [T, H * Dv].
 VM_API int vm_attention_biased_prefill_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table,
                                             int max_blocks, const int* positions, const int* cu_tokens, int B, int n_tiles, const float* rel,
                                             const int* bucket_of, int far, int rel_rows, void* out, int H, int Hkv, int Dk, int Dv, float scale,
                                             int window, int keep_first, int n_pages, int* err, cudaStream_t stream) {
+    return vm_attention_sink_prefill_bf16(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, cu_tokens, B, n_tiles, rel, bucket_of, far,
+                                          rel_rows, nullptr, 0, out, H, Hkv, Dk, Dv, scale, window, keep_first, n_pages, err, stream);
+}
+
+// The same with a sink (float32 [H], null: none; exp(sink[h]) joins head h's denominator) and, with vpages == kpages and
+// v_row_stride == Dk, values that are the first Dv values of the key rows (sizes: vm_attention_sink_prefill_fits).
+VM_API int vm_attention_sink_prefill_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table,
+                                          int max_blocks, const int* positions, const int* cu_tokens, int B, int n_tiles, const float* rel,
+                                          const int* bucket_of, int far, int rel_rows, const float* sink, int v_row_stride, void* out, int H, int Hkv,
+                                          int Dk, int Dv, float scale, int window, int keep_first, int n_pages, int* err, cudaStream_t stream) {
     if (n_tiles <= 0 || B <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || (q_row_stride % 8) != 0 || window < 0 || keep_first < 0) return VM_ERR_UNSUPPORTED;
     if ((rel != nullptr) != (bucket_of != nullptr) || (rel && (far < 0 || rel_rows <= 0))) return VM_ERR_BAD_ARG;
-#define VM_BP(K, V)                                                                                                                        \
-    if (Dk == K && Dv == V)                                                                                                                \
-        return launch_biased_prefill<K, V>(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, cu_tokens, B, n_tiles, rel, \
-                                           bucket_of, far, rel_rows, out, H, Hkv, scale, window, keep_first, n_pages, err, stream);
-    VM_BP(32, 16) VM_BP(32, 32) VM_BP(32, 64) VM_BP(32, 128)
-    VM_BP(64, 16) VM_BP(64, 32) VM_BP(64, 64) VM_BP(64, 128)
-    VM_BP(96, 16) VM_BP(96, 32) VM_BP(96, 64) VM_BP(96, 128)
-    VM_BP(128, 16) VM_BP(128, 32) VM_BP(128, 64) VM_BP(128, 128)
+    const bool in_keys = vpages == kpages && v_row_stride == Dk && Dv < Dk;
+    if (!in_keys && v_row_stride != 0 && v_row_stride != Dv) return VM_ERR_UNSUPPORTED;
+#define VM_BP(K, V, IN)                                                                                                                        \
+    if (Dk == K && Dv == V && in_keys == IN)                                                                                                   \
+        return launch_biased_prefill<K, V, IN>(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, cu_tokens, B, n_tiles, rel, \
+                                               bucket_of, far, rel_rows, out, H, Hkv, scale, window, keep_first, n_pages, sink, err, stream);
+    VM_BP(32, 16, false) VM_BP(32, 32, false) VM_BP(32, 64, false) VM_BP(32, 128, false)
+    VM_BP(64, 16, false) VM_BP(64, 32, false) VM_BP(64, 64, false) VM_BP(64, 128, false)
+    VM_BP(96, 16, false) VM_BP(96, 32, false) VM_BP(96, 64, false) VM_BP(96, 128, false)
+    VM_BP(128, 16, false) VM_BP(128, 32, false) VM_BP(128, 64, false) VM_BP(128, 128, false)
+    VM_BP(32, 16, true) VM_BP(48, 16, true) VM_BP(80, 16, true)
+    VM_BP(48, 32, true) VM_BP(64, 32, true) VM_BP(96, 32, true)
+    VM_BP(80, 64, true) VM_BP(96, 64, true) VM_BP(128, 64, true)
+    VM_BP(144, 128, true) VM_BP(160, 128, true) VM_BP(192, 128, true)
 #undef VM_BP
     return VM_ERR_UNSUPPORTED;
 }
@@ -405,10 +441,21 @@ VM_API int vm_attention_biased_decode_bf16(const void* q, int q_row_stride, cons
                                            int max_blocks, const int* positions, const float* rel, const int* bucket_of, int far, void* out, int B,
                                            int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages, int* err,
                                            cudaStream_t stream) {
+    return vm_attention_sink_decode_bf16(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, rel, bucket_of, far, nullptr, 0, out, B, H, Hkv,
+                                         Dk, Dv, scale, window, keep_first, n_pages, err, stream);
+}
+
+// the same with a sink and a stride between value rows (0: Dv), as vm_attention_sink_generic
+VM_API int vm_attention_sink_decode_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table,
+                                         int max_blocks, const int* positions, const float* rel, const int* bucket_of, int far, const float* sink,
+                                         int v_row_stride, void* out, int B, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first,
+                                         int n_pages, int* err, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || Dk <= 0 || Dk > 1024 || Dv <= 0 || Dv > 256 || window < 0 || keep_first < 0) return VM_ERR_UNSUPPORTED;
     if ((rel != nullptr) != (bucket_of != nullptr) || (rel && far < 0)) return VM_ERR_BAD_ARG;
     if (H > 65535) return VM_ERR_UNSUPPORTED;
+    const int v_stride = v_row_stride > 0 ? v_row_stride : Dv;
+    if (v_stride < Dv || ((Dv % 2) == 0 && (v_stride % 2) != 0)) return VM_ERR_BAD_ARG;
     const size_t smem = ((size_t)((Dk + 3) & ~3) + (size_t)DEC_WARPS * (Dv + 2)) * sizeof(float);
     const dim3 grid(B, H);
     cudaError_t e;
@@ -416,7 +463,7 @@ VM_API int vm_attention_biased_decode_bf16(const void* q, int q_row_stride, cons
     case V:                                                                                                                                   \
         e = vm_launch_pdl(attn_biased_decode_kernel<V>, grid, dim3(DEC_WARPS * 32), smem, stream, (const __nv_bfloat16*)q, q_row_stride,      \
                           (const __nv_bfloat16*)kpages, (const __nv_bfloat16*)vpages, block_table, max_blocks, positions, rel, bucket_of, far, \
-                          (__nv_bfloat16*)out, H, Hkv, Dk, Dv, scale, window, keep_first, n_pages, err);                                      \
+                          (__nv_bfloat16*)out, H, Hkv, Dk, Dv, scale, window, keep_first, n_pages, sink, v_stride, err);                       \
         break;
     switch ((Dv + 63) / 64) {
         VM_BD(1) VM_BD(2) VM_BD(3) VM_BD(4)

@@ -12,7 +12,7 @@ VM_API void vm_set_pdl(int on) { vm_pdl_enabled = on ? 1 : 0; }
 // kernel still refuses an id outside the table (writes zeros and raises the error word).
 template <typename W>
 __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ tokens,
-                                    float* __restrict__ out, int T, int hid, int vocab, int* __restrict__ err) {
+                                    float* __restrict__ out, int T, int hid, int vocab, float scale, int* __restrict__ err) {
     vm_pdl_launch_dependents();
     vm_pdl_wait();
     const int t = blockIdx.x;
@@ -21,20 +21,26 @@ __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __re
     if (!ok && threadIdx.x == 0 && err) atomicExch(err, 1);
     const W* row = table + (size_t)(ok ? id : 0) * hid;
     for (int i = threadIdx.x; i < hid; i += blockDim.x)
-        out[(size_t)t * hid + i] = ok ? vm_to_float(row[i]) : 0.f;
+        out[(size_t)t * hid + i] = ok ? vm_to_float(row[i]) * scale : 0.f;
+}
+
+// (the table's rows times `scale`, in float32)
+VM_API int vm_embed_gather_scaled(const void* table, int table_dtype, const int* tokens, float* out, int T, int hid,
+                                  int vocab, float scale, int* err, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int threads = hid >= 512 ? 256 : 128;
+    if (table_dtype == VM_F32)
+        vm_launch_pdl(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, tokens, out, T, hid, vocab, scale, err);
+    else if (table_dtype == VM_BF16)
+        vm_launch_pdl(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, out, T, hid, vocab, scale, err);
+    else
+        return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
 }
 
 VM_API int vm_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int T, int hid,
                            int vocab, int* err, cudaStream_t stream) {
-    if (T <= 0) return 0;
-    const int threads = hid >= 512 ? 256 : 128;
-    if (table_dtype == VM_F32)
-        vm_launch_pdl(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)table, tokens, out, T, hid, vocab, err);
-    else if (table_dtype == VM_BF16)
-        vm_launch_pdl(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)table, tokens, out, T, hid, vocab, err);
-    else
-        return VM_ERR_UNSUPPORTED;
-    return vm_launch_status();
+    return vm_embed_gather_scaled(table, table_dtype, tokens, out, T, hid, vocab, 1.0f, err, stream);
 }
 
 // ---------------------------------------------------------------- h (+= delta); out = rmsnorm(h) * w

@@ -195,7 +195,7 @@ __global__ void router_kernel(const void* __restrict__ x, const float* __restric
 template <typename T>
 __global__ void router_scored_kernel(const void* __restrict__ x, const float* __restrict__ norm_w, float eps, const float* __restrict__ w_router,
                                      const float* __restrict__ correction, int hidden, int n_out, int top, int group_count, int group_keep,
-                                     float scale, int* __restrict__ chosen, float* __restrict__ weight) {
+                                     float scale, int score_kind, int* __restrict__ chosen, float* __restrict__ weight) {
     __shared__ float red[32];
     extern __shared__ __align__(16) float sm[];          // [hidden] input, [n_out] scores, [n_out] choice scores, [group_count] group scores
     float* xs = sm;
@@ -212,17 +212,25 @@ __global__ void router_scored_kernel(const void* __restrict__ x, const float* __
     }
     __syncthreads();
     if (warp != 0) return;
-    float mx = -INFINITY;
-    for (int e = lane; e < n_out; e += 32) mx = fmaxf(mx, sc[e]);
-    mx = vm_warp_max(mx);
-    float sum = 0.f;
-    for (int e = lane; e < n_out; e += 32) sum += expf(sc[e] - mx);
-    sum = vm_warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < n_out; e += 32) {
-        const float p = expf(sc[e] - mx) * inv;
-        sc[e] = p;
-        ch[e] = p + (correction ? correction[e] : 0.f);
+    if (score_kind == VM_SCORE_SIGMOID) {                 // every output scored alone: s = 1 / (1 + exp(-z))
+        for (int e = lane; e < n_out; e += 32) {
+            const float p = 1.0f / (1.0f + expf(-sc[e]));
+            sc[e] = p;
+            ch[e] = p + (correction ? correction[e] : 0.f);
+        }
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < n_out; e += 32) mx = fmaxf(mx, sc[e]);
+        mx = vm_warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < n_out; e += 32) sum += expf(sc[e] - mx);
+        sum = vm_warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < n_out; e += 32) {
+            const float p = expf(sc[e] - mx) * inv;
+            sc[e] = p;
+            ch[e] = p + (correction ? correction[e] : 0.f);
+        }
     }
     __syncwarp();
     if (group_count > 1 && group_keep < group_count) {
@@ -273,7 +281,7 @@ template <typename T, typename W>
 __global__ void experts_up_kernel(const void* __restrict__ x, const float* __restrict__ norm_w, float eps, const W* __restrict__ w_up,
                                   const W* __restrict__ w_up_shared, const int* __restrict__ chosen, int hidden, int ff, int ff_shared, int top,
                                   int act_kind, int act_kind_shared, int E_real, int glu, float limit, float alpha, int act_cols,
-                                  T* __restrict__ act) {
+                                  const float* __restrict__ weight, T* __restrict__ act) {
     extern __shared__ __align__(16) float xs[];          // [hidden]
     __shared__ float red[32];
     vm_pdl_launch_dependents();
@@ -289,20 +297,24 @@ __global__ void experts_up_kernel(const void* __restrict__ x, const float* __res
     const W* urow[ROWS_PER_WARP];
     int kind[ROWS_PER_WARP];
     bool routed[ROWS_PER_WARP], skip[ROWS_PER_WARP];
+    float wgt[ROWS_PER_WARP];                             // glu == VM_GLU_SILU_WEIGHTED_INPUT: the routing weight scales the expert's input
     const int per = glu ? 2 * ff : ff;                    // rows of one expert's up matrix
 #pragma unroll
     for (int i = 0; i < ROWS_PER_WARP; ++i) {
         const int r = min(r0 + i, rows - 1);              // (a row past the end repeats the last one and is not stored)
         routed[i] = r < top * ff;
         skip[i] = false;
+        wgt[i] = 1.0f;
         if (routed[i]) {
             int e = chosen[(size_t)t * top + r / ff];
+            if (glu == VM_GLU_SILU_WEIGHTED_INPUT) wgt[i] = weight[(size_t)t * top + r / ff];
             if (e >= E_real) { skip[i] = true; e = 0; }   // an identity expert has no rows: zeros
             wrow[i] = w_up + ((size_t)e * per + r % ff) * hidden;
             urow[i] = wrow[i] + (size_t)ff * hidden;
             kind[i] = act_kind;
         } else {
             wrow[i] = urow[i] = w_up_shared + (size_t)(r - top * ff) * hidden;
+            if (glu == VM_GLU_SILU_WEIGHTED_INPUT) urow[i] = wrow[i] + (size_t)ff_shared * hidden;      // the shared expert is gated too
             kind[i] = act_kind_shared;
         }
     }
@@ -315,7 +327,11 @@ __global__ void experts_up_kernel(const void* __restrict__ x, const float* __res
             if (r0 + i < rows) {
                 float v;
                 if (skip[i]) v = 0.f;
-                else if (glu && routed[i]) v = glu_clamped(vm_to_float(vm_from_float<T>(d[i])), vm_to_float(vm_from_float<T>(u[i])), limit, alpha);
+                else if (glu == VM_GLU_SILU_WEIGHTED_INPUT) {
+                    // W (w x) = w (W x): gate and up as the activation dtype holds them, the weight applied in float32
+                    const float g = wgt[i] * vm_to_float(vm_from_float<T>(d[i])), uu = wgt[i] * vm_to_float(vm_from_float<T>(u[i]));
+                    v = g / (1.0f + expf(-g)) * uu;
+                } else if (glu && routed[i]) v = glu_clamped(vm_to_float(vm_from_float<T>(d[i])), vm_to_float(vm_from_float<T>(u[i])), limit, alpha);
                 else v = expert_act(d[i], kind[i]);
                 act[(size_t)t * act_cols + r0 + i] = vm_from_float<T>(v);
             }
@@ -327,7 +343,7 @@ __global__ void experts_up_kernel(const void* __restrict__ x, const float* __res
 template <typename T, typename W>
 __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restrict__ w_down, const W* __restrict__ w_down_shared,
                                     const int* __restrict__ chosen, const float* __restrict__ weight, const float* __restrict__ shared_gate,
-                                    int hidden, int ff, int ff_shared, int top, int E_real, int act_cols, T* __restrict__ out,
+                                    int hidden, int ff, int ff_shared, int top, int E_real, int act_cols, int unit_weights, T* __restrict__ out,
                                     float* __restrict__ residual) {
     extern __shared__ __align__(16) float as[];          // [act_cols]: top * ff + ff_shared, then (identity experts) the input row
     vm_pdl_launch_dependents();
@@ -352,7 +368,7 @@ __global__ void experts_down_kernel(const T* __restrict__ act, const W* __restri
 #pragma unroll
         for (int i = 0; i < ROWS_PER_WARP; ++i) wrow[i] = w_down + ((size_t)e * hidden + min(c0 + i, hidden - 1)) * ff;
         warp_dot_rows<W, ROWS_PER_WARP>(wrow, as + k * ff, ff, lane, d);
-        const float wk = weight[(size_t)t * top + k];
+        const float wk = unit_weights ? 1.0f : weight[(size_t)t * top + k];      // (the weight went into the expert's input)
 #pragma unroll
         for (int i = 0; i < ROWS_PER_WARP; ++i) y[i] = fmaf(wk, d[i], y[i]);
     }
@@ -397,11 +413,12 @@ int launch_experts(const void* x, const float* norm_w, float eps, const void* w_
     const int per_block = warps * ROWS_PER_WARP;
     vm_launch_pdl(experts_up_kernel<T, W>, dim3((rows + per_block - 1) / per_block, T_), dim3(warps * 32), (size_t)hidden * sizeof(float), stream, x, norm_w, eps,
                   (const W*)w_up, (const W*)w_up_shared, chosen, hidden, ff, ff_shared, top, act_kind, act_kind_shared, E_real, glu, limit, alpha, act_cols,
-                  (T*)act);
+                  weight, (T*)act);
     int st = vm_launch_status();
     if (st) return st;
     vm_launch_pdl(experts_down_kernel<T, W>, dim3((hidden + per_block - 1) / per_block, T_), dim3(warps * 32), down_smem, stream, (const T*)act,
-                  (const W*)w_down, (const W*)w_down_shared, chosen, weight, shared_gate, hidden, ff, ff_shared, top, E_real, act_cols, (T*)out, residual);
+                  (const W*)w_down, (const W*)w_down_shared, chosen, weight, shared_gate, hidden, ff, ff_shared, top, E_real, act_cols,
+                  glu == VM_GLU_SILU_WEIGHTED_INPUT ? 1 : 0, (T*)out, residual);
     return vm_launch_status();
 }
 
@@ -469,17 +486,26 @@ VM_API int vm_experts_few_tokens(const void* x, const float* norm_w, float eps, 
 VM_API int vm_expert_router_scored(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
                                    int n_out, int top, int group_count, int group_keep, float scale, int* chosen, float* weight, int act_dtype,
                                    cudaStream_t stream) {
+    return vm_expert_router_scores(x, norm_w, eps, w_router, correction, T, hidden, n_out, top, group_count, group_keep, scale, VM_SCORE_SOFTMAX, chosen,
+                                   weight, act_dtype, stream);
+}
+
+// the same with the kind of score as an argument: VM_SCORE_SOFTMAX over all outputs, or VM_SCORE_SIGMOID of each output alone
+VM_API int vm_expert_router_scores(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
+                                   int n_out, int top, int group_count, int group_keep, float scale, int score_kind, int* chosen, float* weight,
+                                   int act_dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (score_kind != VM_SCORE_SOFTMAX && score_kind != VM_SCORE_SIGMOID) return VM_ERR_BAD_ARG;
     if (n_out <= 0 || top <= 0 || hidden <= 0 || group_count <= 0 || n_out % group_count || group_keep <= 0 || group_keep > group_count) return VM_ERR_BAD_ARG;
     if (top > (n_out / group_count) * group_keep) return VM_ERR_BAD_ARG;
     const size_t smem = (size_t)(hidden + 2 * n_out + group_count) * sizeof(float);
     if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
     if (act_dtype == VM_F32)
         vm_launch_pdl(router_scored_kernel<float>, dim3(T), dim3(256), smem, stream, x, norm_w, eps, w_router, correction, hidden, n_out, top, group_count,
-                      group_keep, scale, chosen, weight);
+                      group_keep, scale, score_kind, chosen, weight);
     else if (act_dtype == VM_BF16)
         vm_launch_pdl(router_scored_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, x, norm_w, eps, w_router, correction, hidden, n_out, top,
-                      group_count, group_keep, scale, chosen, weight);
+                      group_count, group_keep, scale, score_kind, chosen, weight);
     else return VM_ERR_UNSUPPORTED;
     return vm_launch_status();
 }

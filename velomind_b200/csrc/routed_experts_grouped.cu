@@ -157,6 +157,27 @@ experts_down_grouped_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bf
     });
 }
 
+// act[row, i] = silu(w g) (w u) with g = gate_up[row, i], u = gate_up[row, ff + i] and w the routing weight of the row's (token, expert)
+// pair: the weight scales the expert's INPUT, and W (w x) = w (W x).  Rows of padding give zeros.
+__global__ void silu_weighted_rows_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ act, int rows, int ff,
+                                          const int* __restrict__ token_of_row, const int* __restrict__ row_of_pair, const float* __restrict__ weight,
+                                          int top) {
+    const size_t n = (size_t)rows * ff;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const int row = (int)(i / ff), c = (int)(i - (size_t)row * ff);
+        const int tok = token_of_row[row];
+        float v = 0.f;
+        if (tok >= 0) {
+            float w = 0.f;
+            for (int k = 0; k < top; ++k)
+                if (row_of_pair[(size_t)tok * top + k] == row) w = weight[(size_t)tok * top + k];
+            const float g = w * __bfloat162float(gate_up[(size_t)row * 2 * ff + c]), u = w * __bfloat162float(gate_up[(size_t)row * 2 * ff + ff + c]);
+            v = g / (1.0f + expf(-g)) * u;
+        }
+        act[i] = __float2bfloat16_rn(v);
+    }
+}
+
 // (x and chosen given: a pair whose index is E or more is an identity expert, its result the token's input row)
 __global__ void experts_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair, const float* __restrict__ weight,
                                        const float* __restrict__ shared_y, const float* __restrict__ shared_gate, int T, int hidden, int top,
@@ -167,7 +188,7 @@ __global__ void experts_combine_kernel(const float* __restrict__ y, const int* _
         float acc = 0.f;
         for (int k = 0; k < top; ++k) {
             const int row = row_of_pair[(size_t)t * top + k];
-            if (row >= 0) acc = fmaf(weight[(size_t)t * top + k], y[(size_t)row * hidden + c], acc);
+            if (row >= 0) acc = fmaf(weight ? weight[(size_t)t * top + k] : 1.0f, y[(size_t)row * hidden + c], acc);
             else if (x && chosen[(size_t)t * top + k] >= E) acc = fmaf(weight[(size_t)t * top + k], __bfloat162float(x[i]), acc);
         }
         if (shared_y) acc = fmaf(shared_gate ? shared_gate[t] : 1.0f, shared_y[i], acc);
@@ -273,7 +294,13 @@ VM_API int vm_experts_grouped_glu(const void* x, const void* w_up, const void* w
         st = vm_launch_status();
         if (st) return st;
     }
-    if (glu) {
+    if (glu == VM_GLU_SILU_WEIGHTED_INPUT) {
+        const size_t n = (size_t)rows * ff, want = n / 256 + 1;
+        silu_weighted_rows_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, rows, ff,
+                                                                                               token_of_row, row_of_pair, weight, top);
+        st = vm_launch_status();
+        if (st) return st;
+    } else if (glu) {
         const size_t n = (size_t)rows * ff, want = ((ff & 7) == 0 ? n / 8 : n) / 256 + 1;
         glu_rows_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, n, ff, limit, alpha);
         st = vm_launch_status();
@@ -290,7 +317,9 @@ VM_API int vm_experts_grouped_glu(const void* x, const void* w_up, const void* w
     }
     const size_t n = (size_t)T * hidden;
     const size_t want = (n + 255) / 256;
-    experts_combine_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(y, row_of_pair, weight, shared_y, shared_gate, T, hidden, top,
+    // (a weight that went into the expert's input is not applied again)
+    experts_combine_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>(y, row_of_pair, glu == VM_GLU_SILU_WEIGHTED_INPUT ? nullptr : weight,
+                                                                                         shared_y, shared_gate, T, hidden, top,
                                                                                          n_identity > 0 ? (const __nv_bfloat16*)x : nullptr, chosen, E,
                                                                                          (__nv_bfloat16*)out);
     return vm_launch_status();

@@ -494,29 +494,31 @@ void attention(StepContext& ctx, const void* q, int q_row_stride, const KVView& 
 void attention_biased(StepContext& ctx, const void* q, int q_row_stride, const KVView& kv, void* out, int H, int Hkv, int Dk, int Dv, float scale,
                       const BiasedMask& mask) {
     cudaStream_t s = ctx.stream;
+    const bool in_keys = mask.v_row_stride == Dk && kv.v_pages == kv.k_pages && Dv < Dk;
+    if (mask.v_row_stride != 0 && mask.v_row_stride != Dv && !in_keys) throw KernelError("attention: values with a row stride of their own must lie inside the key rows");
     // Which kernel follows from the step's SHAPE and dtype alone, never from its lengths: a recorded step keeps its choice.
     if (ctx.act_dtype == DType::BF16 && ctx.one_token_each && Dk <= 1024 && Dv <= 256 && H <= 65535) {
         Timed t("attention_biased_decode_bf16", s);
-        check(vm_attention_biased_decode_bf16(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, mask.rel,
-                                              mask.bucket_of, mask.far, out, ctx.B, H, Hkv, Dk, Dv, scale, mask.window, mask.keep_first, kv.n_pages,
-                                              ctx.err, s),
+        check(vm_attention_sink_decode_bf16(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, mask.rel, mask.bucket_of,
+                                            mask.far, mask.sink, mask.v_row_stride, out, ctx.B, H, Hkv, Dk, Dv, scale, mask.window, mask.keep_first,
+                                            kv.n_pages, ctx.err, s),
               "attention_biased_decode_bf16", s);
         return;
     }
-    if (ctx.act_dtype == DType::BF16 && vm_attention_biased_prefill_fits(Dk, Dv) && q_row_stride % 8 == 0 && H <= 65535) {
+    if (ctx.act_dtype == DType::BF16 && vm_attention_sink_prefill_fits(Dk, Dv, in_keys ? 1 : 0) && q_row_stride % 8 == 0 && H <= 65535) {
         long long tiles = 0;
         for (int b = 0; b < ctx.B; ++b) tiles += (ctx.host_cu_tokens[b + 1] - ctx.host_cu_tokens[b] + 63) / 64;
         Timed t("attention_biased_prefill_bf16", s);
-        check(vm_attention_biased_prefill_bf16(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, ctx.cu_tokens,
-                                               ctx.B, static_cast<int>(tiles), mask.rel, mask.bucket_of, mask.far, mask.rows, out, H, Hkv, Dk, Dv, scale,
-                                               mask.window, mask.keep_first, kv.n_pages, ctx.err, s),
+        check(vm_attention_sink_prefill_bf16(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, ctx.cu_tokens, ctx.B,
+                                             static_cast<int>(tiles), mask.rel, mask.bucket_of, mask.far, mask.rows, mask.sink, mask.v_row_stride, out, H,
+                                             Hkv, Dk, Dv, scale, mask.window, mask.keep_first, kv.n_pages, ctx.err, s),
               "attention_biased_prefill_bf16", s);
         return;
     }
     Timed t("attention_biased_generic", s);
-    check(vm_attention_biased_generic(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, ctx.seq_of_token, mask.rel,
-                                      mask.bucket_of, mask.far, out, ctx.T, H, Hkv, Dk, Dv, scale, mask.window, mask.keep_first, kv.n_pages,
-                                      code(ctx.act_dtype), ctx.err, s),
+    check(vm_attention_sink_generic(q, q_row_stride, kv.k_pages, kv.v_pages, kv.block_table, kv.table_width, ctx.positions, ctx.seq_of_token, mask.rel,
+                                    mask.bucket_of, mask.far, mask.sink, mask.v_row_stride, out, ctx.T, H, Hkv, Dk, Dv, scale, mask.window, mask.keep_first,
+                                    kv.n_pages, code(ctx.act_dtype), ctx.err, s),
           "attention_biased_generic", s);
 }
 

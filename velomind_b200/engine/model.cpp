@@ -49,7 +49,7 @@ Layer::Layer(const BlockSpec& s) : spec(s) {
     parts.feed_forward = build_part_as<FeedForward>("feed_forward", s.feed_forward);
     parts.mixer_norm = build_part_as<Norm>("norm", s.mixer_norm);
     parts.feed_forward_norm = build_part_as<Norm>("norm", s.feed_forward_norm);
-    block = build_arrangement(s.arrangement, json::Value(), parts);
+    block = build_arrangement(s.arrangement, s.arrangement_args, parts);
 }
 
 std::vector<std::pair<std::string, Part*>> Layer::named_parts() const {
@@ -60,7 +60,8 @@ std::vector<std::pair<std::string, Part*>> Layer::named_parts() const {
     return {{sub("mixer"), parts.mixer.get()},
             {sub("feed_forward"), parts.feed_forward.get()},
             {sub("mixer_norm"), parts.mixer_norm.get()},
-            {sub("feed_forward_norm"), parts.feed_forward_norm.get()}};
+            {sub("feed_forward_norm"), parts.feed_forward_norm.get()},
+            {spec.prefix, block.get()}};               // tensors of the wiring itself, if it has any
 }
 
 // ------------------------------------------------------------------------------------------------ DecoderModel
@@ -111,7 +112,14 @@ bool DecoderModel::graph_safe() const {
 
 std::vector<CacheNeed> DecoderModel::cache_needs() const {
     std::vector<CacheNeed> out;
-    for (const ScheduleEntry& e : plan.schedule) out.push_back(e.cache_of >= 0 ? CacheNeed{} : layers[e.layer].parts.mixer->cache_need());
+    for (const ScheduleEntry& e : plan.schedule) {
+        const Layer& l = layers[e.layer];
+        const int wiring = l.block->state_floats();      // what the wiring keeps per sequence lies behind the mixer's own state
+        if (wiring > 0 && e.cache_of >= 0) throw ConfigError("a layer whose wiring keeps state of its own cannot read another run's cache");
+        CacheNeed need = e.cache_of >= 0 ? CacheNeed{} : l.parts.mixer->cache_need();
+        need.state_floats += wiring;
+        out.push_back(need);
+    }
     return out;
 }
 

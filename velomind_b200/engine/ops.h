@@ -53,9 +53,45 @@ struct Timed {                      // brackets one launch with events when op t
     ~Timed() { if (op_times_active()) op_time_end(name, stream); }
 };
 
-inline void embed_gather(const DeviceTensor& table, const int* tokens, float* out, int T, int hid, int* err, cudaStream_t s) {
+inline void embed_gather(const DeviceTensor& table, const int* tokens, float* out, int T, int hid, float scale, int* err, cudaStream_t s) {
     Timed t("embed_gather", s);
-    check(vm_embed_gather(table.ptr, code(table.dtype), tokens, out, T, hid, static_cast<int>(table.rows()), err, s), "embed_gather", s);
+    check(vm_embed_gather_scaled(table.ptr, code(table.dtype), tokens, out, T, hid, static_cast<int>(table.rows()), scale, err, s), "embed_gather", s);
+}
+
+// what a sublayer reads: h + conv(h), a short causal convolution over time on every channel; the kept inputs live in the running
+// schedule position's state area at `state_offset`
+inline void input_conv(const float* h, const float* taps, int K, int state_offset, StepContext& ctx, void* out) {
+    Timed t("input_conv", ctx.stream);
+    if (K > 1 && (!ctx.state() || ctx.state_floats() < state_offset + (K - 1) * ctx.hidden))
+        throw CacheError("input convolution: the cache holds no state area for this layer's kept inputs");
+    check(vm_input_conv(h, taps, ctx.state(), ctx.state_floats(), state_offset, ctx.positions, ctx.seq_of_token, ctx.cu_tokens, ctx.slots, out, ctx.T, ctx.B,
+                        ctx.hidden, K, ctx.one_token_each ? 1 : 0, code(ctx.act_dtype), ctx.stream),
+          "input_conv", ctx.stream);
+    if (!ctx.one_token_each && K > 1) ++counters().own_launches;      // two kernels
+}
+
+// h += rmsnorm(y) * w: the residual sum of a sublayer whose norm sits on its output
+inline void norm_residual_add(float* h, const void* y, long long ld, DType y_dtype, const float* w, float eps, int T, int hid, cudaStream_t s) {
+    Timed t("norm_residual_add", s);
+    check(vm_norm_residual_add(h, y, ld, code(y_dtype), w, T, hid, eps, s), "norm_residual_add", s);
+}
+
+inline void polynorm(const void* z, DType z_dtype, const float* coef, void* out, int T, int n, float eps, DType act, cudaStream_t s) {
+    Timed t("polynorm", s);
+    check(vm_polynorm(z, code(z_dtype), coef, out, T, n, eps, code(act), s), "polynorm", s);
+}
+
+inline void rotate_slice(const void* src, long long src_ld, int src_head, int src_off, void* dst, long long dst_ld, int dst_head, int dst_off,
+                         const RotaryTable& rot, int width, int H, const StepContext& ctx) {
+    Timed t("rotate_slice", ctx.stream);
+    check(vm_rotate_slice(src, src_ld, src_head, src_off, dst, dst_ld, dst_head, dst_off, ctx.positions, rot.inv_freq, rot.inv_freq ? rot.rotary_dim : 0,
+                          rot.pairing, width, H, ctx.T, code(ctx.act_dtype), ctx.stream),
+          "rotate_slice", ctx.stream);
+}
+
+inline void sigmoid_gate(void* x, const float* gate, long long gate_ld, int T, int cols, DType act, cudaStream_t s) {
+    Timed t("sigmoid_gate", s);
+    check(vm_sigmoid_gate(x, gate, gate_ld, T, cols, code(act), s), "sigmoid_gate", s);
 }
 
 inline void add_rmsnorm(float* h, const void* delta, const float* weight, float eps, void* out, const int* rows, int n_out, int hid, DType act,
@@ -97,6 +133,16 @@ inline void latent_norm_write(const float* down, int ld, int q_rank, int kv_rank
     Timed t("latent_norm_write", ctx.stream);
     check(vm_latent_norm_write(down, ld, q_rank, kv_rank, wq, wkv, eps, cq, ctx.positions, ctx.seq_of_token, kv.block_table, kv.table_width,
                                write ? kv.k_pages : nullptr, write ? kv.n_pages : 0, ctx.T, code(ctx.act_dtype), ctx.err, ctx.stream),
+          "latent_norm_write", ctx.stream);
+}
+
+// the same with `rot_dim` more values per token behind the latent: the key part all heads share, turned by the token's position
+inline void latent_rope_norm_write(const float* down, int ld, int q_rank, int kv_rank, const float* wq, const float* wkv, float eps, void* cq,
+                                   const StepContext& ctx, const KVView& kv, bool write, int rot_dim, const RotaryTable& rot) {
+    Timed t("latent_norm_write", ctx.stream);
+    check(vm_latent_rope_norm_write(down, ld, q_rank, kv_rank, wq, wkv, eps, cq, ctx.positions, ctx.seq_of_token, kv.block_table, kv.table_width,
+                                    write ? kv.k_pages : nullptr, write ? kv.n_pages : 0, rot_dim, rot.inv_freq ? rot.rotary_dim : 0, rot.inv_freq,
+                                    rot.pairing, ctx.T, code(ctx.act_dtype), ctx.err, ctx.stream),
           "latent_norm_write", ctx.stream);
 }
 
@@ -153,15 +199,16 @@ inline void experts_few_tokens(const void* x, const float* norm_w, float eps, co
 struct ExpertKind {
     int E = 0, n_identity = 0;          // real experts; identity experts behind them in the router's outputs
     int act_kind = VM_ACT_RELU_SQUARED;
-    bool glu = false;                   // gated experts with the clamped unit
+    int glu = VM_GLU_NONE;              // gated experts: VM_GLU_CLAMPED, or VM_GLU_SILU_WEIGHTED_INPUT (the routing weight on the expert's input)
     float limit = 0.f, alpha = 0.f;
 };
 
 inline void expert_router_scored(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
-                                 int n_out, int top, int group_count, int group_keep, float scale, int* chosen, float* weight, DType act,
+                                 int n_out, int top, int group_count, int group_keep, float scale, int score_kind, int* chosen, float* weight, DType act,
                                  cudaStream_t s) {
     Timed t("expert_router", s);
-    check(vm_expert_router_scored(x, norm_w, eps, w_router, correction, T, hidden, n_out, top, group_count, group_keep, scale, chosen, weight, code(act), s),
+    check(vm_expert_router_scores(x, norm_w, eps, w_router, correction, T, hidden, n_out, top, group_count, group_keep, scale, score_kind, chosen, weight,
+                                  code(act), s),
           "expert_router", s);
 }
 
@@ -171,7 +218,7 @@ inline void experts_few_tokens_glu(const void* x, const float* norm_w, float eps
                                    DType act_dtype, cudaStream_t s) {
     Timed t("experts_few_tokens", s);
     check(vm_experts_few_tokens_glu(x, norm_w, eps, up.ptr, down.ptr, up_shared, down_shared, code(up.dtype), chosen, weight, shared_gate, T, hidden, ff,
-                                    ff_shared, top, k.act_kind, act_kind_shared, k.E, k.n_identity, k.glu ? 1 : 0, k.limit, k.alpha, act, out, residual,
+                                    ff_shared, top, k.act_kind, act_kind_shared, k.E, k.n_identity, k.glu, k.limit, k.alpha, act, out, residual,
                                     code(act_dtype), s),
           "experts_few_tokens", s);
     ++counters().own_launches;          // two kernels
@@ -183,7 +230,7 @@ inline void experts_grouped_glu(const void* x, const DeviceTensor& up, const Dev
                                 int* err, cudaStream_t s) {
     Timed t(x_sorted ? "experts_grouped_tc" : "experts_grouped", s);
     check(vm_experts_grouped_glu(x, up.ptr, down.ptr, chosen, weight, shared_y, shared_gate, T, hidden, ff, top, k.E, k.n_identity, k.act_kind,
-                                 k.glu ? 1 : 0, k.limit, k.alpha, row_cap, row_of_pair, token_of_row, expert_of_tile, x_sorted, act, gate_up, y, out, err, s),
+                                 k.glu, k.limit, k.alpha, row_cap, row_of_pair, token_of_row, expert_of_tile, x_sorted, act, gate_up, y, out, err, s),
           "experts_grouped", s);
     counters().own_launches += (x_sorted ? 4 : 3) + (k.glu ? 1 : 0);
 }
@@ -202,6 +249,8 @@ struct BiasedMask {
     const float* rel = nullptr;         // device float32 [rows, H], or null: no bias
     const int* bucket_of = nullptr;     // device int32 [far + 1]
     int far = 0, rows = 0, window = 0, keep_first = 0;
+    const float* sink = nullptr;        // device float32 [H], or null: exp(sink[h]) joins head h's softmax denominator
+    int v_row_stride = 0;               // elements between neighbouring tokens' value rows (0: Dv); Dk with the key pool as value pool: values inside keys
 };
 // attention of the step's tokens over the cache with that mask and bias; keys of Dk, values of Dv; picks the kernel by shape and dtype
 void attention_biased(StepContext& ctx, const void* q, int q_row_stride, const KVView& kv, void* out, int H, int Hkv, int Dk, int Dv, float scale,

@@ -24,6 +24,14 @@ enum { VM_ERR_UNSUPPORTED = -1, VM_ERR_BAD_ARG = -2 };
 enum { VM_PAIR_HALF_SPLIT = 0, VM_PAIR_INTERLEAVED = 1 };
 // activations of the feed-forward kernels: x sigmoid(x); the tanh form of GELU; max(x, 0)^2
 enum { VM_ACT_SILU = 0, VM_ACT_GELU_TANH = 1, VM_ACT_RELU_SQUARED = 2 };
+// not elementwise, so no kernel that takes VM_ACT_* knows it: a polynomial of a token's row and its powers, each divided by its root
+// mean square (vm_polynorm)
+enum { VM_ACT_POLYNORM = 16 };
+// gated experts: the clamped unit min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u) + 1); or silu(w g) (w u) with the routing weight w
+// on the expert's input (it is then not applied to the output again, and the shared expert is gated in the same way, with w = 1)
+enum { VM_GLU_NONE = 0, VM_GLU_CLAMPED = 1, VM_GLU_SILU_WEIGHTED_INPUT = 2 };
+// how a router that scores all its outputs scores them: softmax over all of them, or the sigmoid of each alone
+enum { VM_SCORE_SOFTMAX = 0, VM_SCORE_SIGMOID = 1 };
 // error words a kernel may leave in `err`
 enum { VM_ERRWORD_TOKEN_ID = 1, VM_ERRWORD_CACHE_WRITE = 2, VM_ERRWORD_CACHE_READ = 3, VM_ERRWORD_BARRIER_WAIT = 4 };
 
@@ -31,6 +39,8 @@ enum { VM_ERRWORD_TOKEN_ID = 1, VM_ERRWORD_CACHE_WRITE = 2, VM_ERRWORD_CACHE_REA
 void vm_set_pdl(int on);                      // programmatic dependent launch for the decode chain (default on)
 int vm_embed_gather(const void* table, int table_dtype, const int* tokens, float* out, int T, int hid, int vocab, int* err,
                     cudaStream_t stream);
+int vm_embed_gather_scaled(const void* table, int table_dtype, const int* tokens, float* out, int T, int hid, int vocab, float scale, int* err,
+                           cudaStream_t stream);      // the rows times `scale`
 int vm_add_rmsnorm(float* h, const void* delta, const float* w, void* out, const int* rows, int n_out, int hid, float eps,
                    int act_dtype, cudaStream_t stream);
 int vm_residual_add(float* h, const void* delta, long long n, int act_dtype, cudaStream_t stream);
@@ -45,6 +55,26 @@ int vm_gated_activation(const void* gate_up, void* out, int T, int I, int kind, 
 int vm_latent_norm_write(const float* down, int ld, int q_rank, int kv_rank, const float* wq, const float* wkv, float eps, void* cq,
                          const int* positions, const int* seq_of_token, const int* block_table, int max_blocks, void* pages,
                          int n_pages, int T, int act_dtype, int* err, cudaStream_t stream);
+
+// the same for a layer with rotary positions: rot_dim more columns behind the key/value latent (not normed, one key part shared by all heads)
+// whose first rotary_dim values are turned by the token's position; pages [n_pages, VM_PAGE_TOKENS, kv_rank + rot_dim]
+int vm_latent_rope_norm_write(const float* down, int ld, int q_rank, int kv_rank, const float* wq, const float* wkv, float eps, void* cq,
+                              const int* positions, const int* seq_of_token, const int* block_table, int max_blocks, void* pages, int n_pages,
+                              int rot_dim, int rotary_dim, const float* inv_freq, int pairing, int T, int act_dtype, int* err, cudaStream_t stream);
+
+// ---- sublayer.cu: a layer whose sublayers read the residual stream through a short causal convolution and are normed on their output
+// out [T, hid] (activation dtype) = h + conv(h) over time per channel, taps float32 [hid, K]; the K - 1 last inputs of every sequence are
+// kept in state [slot, state_stride] at state_offset (float32) and moved on by the step's tokens
+int vm_input_conv(const float* h, const float* taps, float* state, long long state_stride, int state_offset, const int* positions,
+                  const int* seq_of_token, const int* cu_tokens, const int* slots, void* out, int T, int B, int hid, int K, int one_token_each,
+                  int act_dtype, cudaStream_t stream);
+int vm_norm_residual_add(float* h, const void* y, long long ld, int y_dtype, const float* w, int T, int hid, float eps, cudaStream_t stream);
+// a N(z) + b N(z^2) + c N(z^3) + e per token, N: division by the root mean square over the token's n values; coef float32 [4]
+int vm_polynorm(const void* z, int z_dtype, const float* coef, void* out, int T, int n, float eps, int act_dtype, cudaStream_t stream);
+int vm_rotate_slice(const void* src, long long src_ld, int src_head, int src_off, void* dst, long long dst_ld, int dst_head, int dst_off,
+                    const int* positions, const float* inv_freq, int rotary_dim, int pairing, int width, int H, int T, int act_dtype,
+                    cudaStream_t stream);
+int vm_sigmoid_gate(void* x, const float* gate, long long gate_ld, int T, int cols, int act_dtype, cudaStream_t stream);
 
 // ---- mlstm.cu: the matrix-memory recurrence with its output stage
 // proj float32 [T, ld]: q | k | v | g | x_i | x_f (H*D, H*D, H*V, H*V, H, H columns); state float32, per slot and head S [D, V], n [D], m;
@@ -88,6 +118,10 @@ int vm_expert_router_scored(const void* x, const float* norm_w, float eps, const
                             int n_out, int top, int group_count, int group_keep, float scale, int* chosen, float* weight, int act_dtype,
                             cudaStream_t stream);
 
+int vm_expert_router_scores(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
+                            int n_out, int top, int group_count, int group_keep, float scale, int score_kind, int* chosen, float* weight, int act_dtype,
+                            cudaStream_t stream);      // vm_expert_router_scored with the kind of score (VM_SCORE_*) as an argument
+
 // ---- attention_biased.cu: windowed attention with kept first tokens and a learned bias by bucketed distance; keys of Dk, values of Dv
 // qkv [T, ld]: H query heads and Hkv key heads of Dk, Hkv value heads of Dv; queries and keys get a unit-rms norm per head (weights wq, wk
 // float32 [Dk]), queries in place, keys and values into the pages (kpages null: none written); v_first [T, Hkv * Dv] is blended into the
@@ -101,6 +135,23 @@ int vm_attention_biased_generic(const void* q, int q_row_stride, const void* kpa
                                 const int* positions, const int* seq_of_token, const float* rel, const int* bucket_of, int far, void* out,
                                 int n_tokens, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages, int act_dtype,
                                 int* err, cudaStream_t stream);
+
+// The same attention with a sink and with values that may lie inside the key rows.  sink float32 [H] (null: none): exp(sink[h]) is one
+// more term of head h's softmax denominator, without a key or a value, not scaled.  v_row_stride: elements between the value rows of
+// neighbouring tokens in `vpages` (0: Dv); with vpages == kpages and v_row_stride == Dk a token's value is the first Dv values of its key row.
+int vm_attention_sink_generic(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table, int max_blocks,
+                              const int* positions, const int* seq_of_token, const float* rel, const int* bucket_of, int far, const float* sink,
+                              int v_row_stride, void* out, int n_tokens, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first,
+                              int n_pages, int act_dtype, int* err, cudaStream_t stream);
+int vm_attention_sink_prefill_fits(int Dk, int Dv, int values_in_keys);
+int vm_attention_sink_prefill_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table, int max_blocks,
+                                   const int* positions, const int* cu_tokens, int B, int n_tiles, const float* rel, const int* bucket_of, int far,
+                                   int rel_rows, const float* sink, int v_row_stride, void* out, int H, int Hkv, int Dk, int Dv, float scale, int window,
+                                   int keep_first, int n_pages, int* err, cudaStream_t stream);
+int vm_attention_sink_decode_bf16(const void* q, int q_row_stride, const void* kpages, const void* vpages, const int* block_table, int max_blocks,
+                                  const int* positions, const float* rel, const int* bucket_of, int far, const float* sink, int v_row_stride, void* out,
+                                  int B, int H, int Hkv, int Dk, int Dv, float scale, int window, int keep_first, int n_pages, int* err,
+                                  cudaStream_t stream);
 
 // ---- attention_biased_fast.cu: the same attention in bfloat16: prompts on mma.sync tiles (keys and values of the sizes that
 // vm_attention_biased_prefill_fits names; n_tiles = sum over the sequences of ceil(new tokens / 64)), decode steps (token s is sequence s's)

@@ -160,6 +160,7 @@ struct PartSpec {
 // One layer: an arrangement (how norms, mixer, feed-forward and residual are wired) and its parts.
 struct BlockSpec {
     std::string arrangement;                  // registry kind of the wiring, e.g. "prenorm"
+    json::Value arrangement_args;             // the wiring's own sizes and constants (null: none); its tensors hang directly under `prefix`
     std::string prefix;                       // weight-name prefix of this layer in the checkpoint
     PartSpec mixer, feed_forward, mixer_norm, feed_forward_norm;
     std::map<std::string, std::string> names; // part -> sub-prefix, e.g. {"mixer": "self_attn."}
@@ -546,6 +547,9 @@ public:
     // wires norms, parts and the residual; `pending` is a delta (activation dtype) not yet added to h, or null;
     // returns the delta this layer leaves pending (a workspace buffer the caller gives back), or null
     virtual void* forward(StepContext& ctx, float* h, void* pending) = 0;
+    // float32 values the wiring itself keeps per sequence (the last inputs of a convolution over time); they lie behind the mixer's
+    // own state in the run's state area, at offset mixer->cache_need().state_floats
+    virtual int state_floats() const { return 0; }
 };
 
 class Embedding : public Part {

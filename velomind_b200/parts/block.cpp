@@ -55,6 +55,73 @@ private:
     bool feed_forward_;
 };
 
+// h += norm(mixer(in(h))); h += norm(feed_forward(in(h))): the sublayers read the residual stream itself and the norm sits on
+// each sublayer's OUTPUT.  in(h) = h + conv(h) when `taps` >= 1: a causal convolution over time on every channel,
+//   conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j)     (tensors `mixer_conv` and `feed_forward_conv`, [hidden, taps], no bias),
+// zeros before a sequence's start; with taps = 0 in(h) = h.  The last taps - 1 inputs of either
+// convolution are part of a sequence's state: they live in the run's float32 state area behind the mixer's own state, and
+// move on with every step.  Residual stream, convolution and norm are float32; what the sublayer reads is rounded to the
+// activation dtype once.
+class OutputNormBlock : public Arrangement {
+public:
+    OutputNormBlock(const BlockParts& p, int hidden, int taps, std::string mixer_conv, std::string ff_conv, bool feed_forward)
+        : p_(p), hidden_(hidden), K_(taps < 0 ? 0 : taps), mixer_conv_(std::move(mixer_conv)), ff_conv_(std::move(ff_conv)), feed_forward_(feed_forward) {
+        if (hidden <= 0) throw ConfigError("arrangement 'output_norm': argument 'hidden' must be positive");
+        if (K_ > 64) throw ConfigError(format("arrangement 'output_norm': taps (%d) must be within 0..64", K_));
+        if (K_ >= 1 && (mixer_conv_.empty() || (feed_forward_ && ff_conv_.empty())))
+            throw ConfigError("arrangement 'output_norm': a convolution needs the names of its tensors");
+    }
+    bool graph_safe() const override { return true; }
+    bool convolves() const { return K_ >= 1; }
+
+    WeightTable weight_specs() const override {
+        WeightTable t;
+        if (!convolves()) return t;
+        t[mixer_conv_].shape = {hidden_, K_};
+        if (feed_forward_) t[ff_conv_].shape = {hidden_, K_};
+        return t;
+    }
+    void bind(const Weights& w, BindContext& bc) override {
+        if (!convolves()) return;
+        taps_mixer_ = bc.upload(w.at(mixer_conv_), DType::F32);
+        if (feed_forward_) taps_ff_ = bc.upload(w.at(ff_conv_), DType::F32);
+    }
+    int state_floats() const override { return convolves() ? (feed_forward_ ? 2 : 1) * (K_ - 1) * hidden_ : 0; }
+
+    void* forward(StepContext& ctx, float* h, void* pending) override {
+        if (ctx.hidden != hidden_) throw ConfigError("arrangement 'output_norm': the stream's width is not the one it was built for");
+        if (pending) {                               // a layer of another wiring left its last sum to its successor
+            ops::residual_add(h, pending, static_cast<long long>(ctx.T) * hidden_, ctx.act_dtype, ctx.stream);
+            ctx.give(pending);
+        }
+        const int base = p_.mixer->cache_need().state_floats;
+        half(ctx, h, taps_mixer_, base, *p_.mixer_norm, [&](const void* x, void* y) { p_.mixer->forward(ctx, x, y); });
+        if (feed_forward_)
+            half(ctx, h, taps_ff_, base + (K_ - 1) * hidden_, *p_.feed_forward_norm, [&](const void* x, void* y) { p_.feed_forward->forward(ctx, x, y); });
+        return nullptr;
+    }
+
+private:
+    template <class Run> void half(StepContext& ctx, float* h, const DeviceTensor& taps, int state_offset, Norm& norm, Run run) {
+        const float* nw = nullptr;
+        float eps = 0.f;
+        if (!norm.as_rms(&nw, &eps)) throw ConfigError("arrangement 'output_norm': the norm on a sublayer's output must be a root-mean-square norm");
+        void* x = ctx.take_tokens(hidden_, ctx.act_dtype);
+        if (convolves()) ops::input_conv(h, static_cast<const float*>(taps.ptr), K_, state_offset, ctx, x);
+        else if (ctx.act_dtype != DType::F32) ops::convert(h, DType::F32, x, ctx.act_dtype, static_cast<long long>(ctx.T) * hidden_, ctx.stream);
+        void* y = ctx.take_tokens(hidden_, ctx.act_dtype);
+        run(convolves() || ctx.act_dtype != DType::F32 ? x : h, y);      // (a float32 sublayer without a convolution reads the stream in place)
+        ctx.give(x);
+        ops::norm_residual_add(h, y, hidden_, ctx.act_dtype, nw, eps, ctx.T, hidden_, ctx.stream);
+        ctx.give(y);
+    }
+    BlockParts p_;
+    int hidden_, K_;
+    std::string mixer_conv_, ff_conv_;
+    bool feed_forward_;
+    DeviceTensor taps_mixer_, taps_ff_;
+};
+
 // The feed-forward of a layer that has none: no weights, never run.
 class NoFeedForward : public FeedForward {
 public:
@@ -68,6 +135,13 @@ struct Reg {
         register_arrangement("prenorm", [](const json::Value&, const BlockParts& parts) { return std::make_shared<PreNormBlock>(parts); });
         // h += mixer(norm(h)) and nothing else: the layer's feed-forward and its norm are parts of kind "none"
         register_arrangement("prenorm_mixer", [](const json::Value&, const BlockParts& parts) { return std::make_shared<PreNormBlock>(parts, false); });
+        // the norm on each sublayer's output, the sublayers reading the stream through an optional short convolution over time
+        register_arrangement("output_norm", [](const json::Value& a, const BlockParts& parts) {
+            const char* k = "output_norm";
+            return std::make_shared<OutputNormBlock>(parts, static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int_or(a, "taps", 0, k)),
+                                                     arg_string_or(a, "mixer_conv", "", k), arg_string_or(a, "feed_forward_conv", "", k),
+                                                     arg_int_or(a, "feed_forward", 1, k) != 0);
+        });
         register_part("feed_forward", "none", [](const json::Value&) { return std::make_shared<NoFeedForward>(); });
     }
 } reg;

@@ -8,7 +8,9 @@ namespace vmb {
 class TokenEmbedding : public Embedding {
 public:
     // `tensor`: what the table is called behind the part's prefix ("weight" unless the checkpoint says otherwise; may be empty)
-    TokenEmbedding(int vocab, int hidden, std::string tensor = "weight") : vocab_(vocab), hidden_(hidden), tensor_(std::move(tensor)) {}
+    // `scale`: every row is multiplied by it on the way into the stream (in float32)
+    TokenEmbedding(int vocab, int hidden, std::string tensor = "weight", float scale = 1.0f)
+        : vocab_(vocab), hidden_(hidden), tensor_(std::move(tensor)), scale_(scale) {}
     WeightTable weight_specs() const override {
         WeightTable t;
         t[tensor_].shape = {vocab_, hidden_};
@@ -16,11 +18,12 @@ public:
     }
     void bind(const Weights& w, BindContext& bc) override { table_ = bc.upload(w.at(tensor_), bc.matrix_dtype({&w.at(tensor_)})); }
     bool graph_safe() const override { return true; }
-    void forward(StepContext& ctx, const int* tokens, float* h) override { ops::embed_gather(table_, tokens, h, ctx.T, hidden_, ctx.err, ctx.stream); }
+    void forward(StepContext& ctx, const int* tokens, float* h) override { ops::embed_gather(table_, tokens, h, ctx.T, hidden_, scale_, ctx.err, ctx.stream); }
 
 private:
     int vocab_, hidden_;
     std::string tensor_;
+    float scale_;
     DeviceTensor table_;
 };
 
@@ -55,7 +58,8 @@ private:
 namespace {
 RegisterPart reg_embed("embedding", "token_table", [](const json::Value& a) {
     return std::make_shared<TokenEmbedding>(static_cast<int>(arg_int(a, "vocab", "token_table")), static_cast<int>(arg_int(a, "hidden", "token_table")),
-                                            arg_string_or(a, "tensor", "weight", "token_table"));
+                                            arg_string_or(a, "tensor", "weight", "token_table"),
+                                            static_cast<float>(arg_number_or(a, "scale", 1.0, "token_table")));
 });
 RegisterPart reg_head("head", "linear", [](const json::Value& a) {
     return std::make_shared<LinearHead>(static_cast<int>(arg_int(a, "vocab", "linear")), static_cast<int>(arg_int(a, "hidden", "linear")),

@@ -99,21 +99,30 @@ private:
 int activation_code(const std::string& name, const char* part);     // parts/routed_experts.cpp
 
 // The two-matrix unit without a gate: down(act(up(x))), no biases; `activation` and the tensors' names are arguments.
+//
+// The activation "polynorm" is not elementwise: a N(z) + b N(z^2) + c N(z^3) + e with the powers taken value by value, N the
+// division of a token's row of `intermediate` values by its root mean square (`eps` inside the root), and a, b, c, e the four
+// numbers of the tensor `coefficients`.  Its sums are float32.
 class PlainMLP : public FeedForward {
 public:
-    PlainMLP(int hidden, int intermediate, int activation, std::string up, std::string down)
-        : hidden_(hidden), I_(intermediate), act_(activation), up_name_(std::move(up)), down_name_(std::move(down)) {}
+    PlainMLP(int hidden, int intermediate, int activation, std::string up, std::string down, std::string coefficients = "", float eps = 0.f)
+        : hidden_(hidden), I_(intermediate), act_(activation), up_name_(std::move(up)), down_name_(std::move(down)), coef_name_(std::move(coefficients)),
+          eps_(eps) {
+        if (act_ == VM_ACT_POLYNORM && coef_name_.empty()) throw ConfigError("part 'mlp': the activation \"polynorm\" needs the name of its tensor of coefficients");
+    }
 
     WeightTable weight_specs() const override {
         WeightTable t;
         t[up_name_].shape = {I_, hidden_};
         t[down_name_].shape = {hidden_, I_};
+        if (act_ == VM_ACT_POLYNORM) t[coef_name_].shape = {4};
         return t;
     }
 
     void bind(const Weights& w, BindContext& bc) override {
         up_.bind({&w.at(up_name_)}, bc);
         down_.bind({&w.at(down_name_)}, bc);
+        if (act_ == VM_ACT_POLYNORM) coef_ = bc.upload(w.at(coef_name_), DType::F32);
     }
 
     bool graph_safe() const override { return true; }
@@ -123,7 +132,7 @@ public:
     bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
         const float* nw;
         float eps;
-        if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16) return false;
+        if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16 || act_ == VM_ACT_POLYNORM) return false;
         if (up_.weight.dtype != DType::BF16 || down_.weight.dtype != DType::BF16) return false;
         if (ctx.T_cap <= max_rows()) return hidden_ % 32 == 0 && I_ % 32 == 0;
         return hidden_ % 8 == 0 && I_ % 8 == 0;
@@ -156,17 +165,37 @@ public:
     }
 
     void forward(StepContext& ctx, const void* x, void* out) override {
+        // few tokens in bfloat16: the weight-streaming products (the first one with a float32 result where the activation sums over the row)
+        const bool few = ctx.act_dtype == DType::BF16 && ctx.T_cap <= max_rows() && up_.weight.dtype == DType::BF16 && down_.weight.dtype == DType::BF16 &&
+                         hidden_ % 32 == 0 && I_ % 32 == 0;
         void* u = ctx.take_tokens(I_, ctx.act_dtype);
-        up_.apply(ctx, x, ctx.act_dtype, u, ctx.act_dtype, ctx.T, ctx.T_cap);
-        ops::activation(u, u, static_cast<long long>(ctx.T) * I_, act_, ctx.act_dtype, ctx.stream);
-        down_.apply(ctx, u, ctx.act_dtype, out, ctx.act_dtype, ctx.T, ctx.T_cap);
+        if (act_ == VM_ACT_POLYNORM) {
+            if (few) {
+                float* z = static_cast<float*>(ctx.take_tokens(I_, DType::F32));
+                ops::skinny_linear(x, nullptr, 0.f, up_.weight, ctx.T, z, I_, true, nullptr, ctx.err, ctx.stream);
+                ops::polynorm(z, DType::F32, static_cast<const float*>(coef_.ptr), u, ctx.T, I_, eps_, ctx.act_dtype, ctx.stream);
+                ctx.give(z);
+            } else {
+                up_.apply(ctx, x, ctx.act_dtype, u, ctx.act_dtype, ctx.T, ctx.T_cap);
+                ops::polynorm(u, ctx.act_dtype, static_cast<const float*>(coef_.ptr), u, ctx.T, I_, eps_, ctx.act_dtype, ctx.stream);
+            }
+        } else if (few) {
+            ops::skinny_linear_act(x, nullptr, 0.f, up_.weight, ctx.T, act_, u, I_, ctx.err, ctx.stream);
+        } else {
+            up_.apply(ctx, x, ctx.act_dtype, u, ctx.act_dtype, ctx.T, ctx.T_cap);
+            ops::activation(u, u, static_cast<long long>(ctx.T) * I_, act_, ctx.act_dtype, ctx.stream);
+        }
+        if (few) ops::skinny_linear(u, nullptr, 0.f, down_.weight, ctx.T, out, hidden_, false, nullptr, ctx.err, ctx.stream);
+        else down_.apply(ctx, u, ctx.act_dtype, out, ctx.act_dtype, ctx.T, ctx.T_cap);
         ctx.give(u);
     }
 
 private:
     int hidden_, I_, act_;
-    std::string up_name_, down_name_;
+    std::string up_name_, down_name_, coef_name_;
+    float eps_;
     Linear up_, down_;
+    DeviceTensor coef_;
 };
 
 namespace {
@@ -183,9 +212,11 @@ RegisterPart reg_gated("feed_forward", "gated", [](const json::Value& a) {
 // the unit without a gate
 RegisterPart reg_mlp("feed_forward", "mlp", [](const json::Value& a) {
     const char* k = "mlp";
+    const std::string act = arg_string_or(a, "activation", "relu_squared", k);
     return std::make_shared<PlainMLP>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "intermediate", k)),
-                                      activation_code(arg_string_or(a, "activation", "relu_squared", k), k), arg_string_or(a, "up", "up", k),
-                                      arg_string_or(a, "down", "down", k));
+                                      act == "polynorm" ? static_cast<int>(VM_ACT_POLYNORM) : activation_code(act, k), arg_string_or(a, "up", "up", k),
+                                      arg_string_or(a, "down", "down", k), arg_string_or(a, "coefficients", "", k),
+                                      static_cast<float>(arg_number_or(a, "eps", 0.0, k)));
 });
 }  // namespace
 

@@ -11,6 +11,15 @@
 // (query heads that share a kv head), so prompts and decode steps use the same kernels as grouped-query attention.
 //
 // A layer may read another run's latents (the schedule's `cache_of`): it then has no W_dkv of its own, and writes nothing.
+//
+// Options, each an argument:
+//   rot_dim > 0 with a `position` part: every query head has rot_dim more values behind its `dim` unrotated ones, and W_dkv has rot_dim
+//     more rows behind the latent's: one key part for all heads, not normed.  Both are turned by the token's position, and
+//     score = scale (q_h . k_h + q_rot,h . k_rot).  A cache row is then [c | k_rot]: with the up-projection on the query's side the
+//     query is [W_uk,h^T q_h | q_rot,h], the key the whole row, the value its first kv_rank values.
+//   window > 0: a query sees itself and the window - 1 tokens before it; the cache gives older pages back.
+//   sink: a learned number per head (tensor `sink`) whose exponential joins the softmax's denominator, without key or value.
+//   gate: the heads' outputs are multiplied by sigmoid(W_g x) (tensor `g`, read from the layer's input) before W_o.
 #include <algorithm>
 #include <cmath>
 
@@ -19,32 +28,50 @@
 
 namespace vmb {
 
+struct LatentOptions {
+    int rot_dim = 0, window = 0;
+    bool sink = false, gate = false;
+    PartSpec position{"none", json::Value()};
+};
+
 class LatentAttention : public Mixer {
 public:
-    LatentAttention(int hidden, int heads, int dim, int vdim, int q_rank, int kv_rank, double scale, double eps, bool own_latent)
-        : hidden_(hidden), H_(heads), D_(dim), V_(vdim), Rq_(q_rank), Rkv_(kv_rank), own_(own_latent),
-          scale_(scale > 0 ? static_cast<float>(scale) : static_cast<float>(1.0 / std::sqrt(static_cast<double>(dim)))), eps_(static_cast<float>(eps)) {}
+    using Options = LatentOptions;
+    LatentAttention(int hidden, int heads, int dim, int vdim, int q_rank, int kv_rank, double scale, double eps, bool own_latent, const Options& o)
+        : hidden_(hidden), H_(heads), D_(dim), V_(vdim), Rq_(q_rank), Rkv_(kv_rank), R_(o.rot_dim), window_(o.window), own_(own_latent), sink_(o.sink),
+          gate_(o.gate), scale_(scale > 0 ? static_cast<float>(scale) : static_cast<float>(1.0 / std::sqrt(static_cast<double>(dim + o.rot_dim)))),
+          eps_(static_cast<float>(eps)), position_(build_part_as<Position>("position", o.position)) {
+        if (R_ < 0 || window_ < 0) throw ConfigError("part 'latent_attention': rot_dim and window must not be negative");
+    }
+    bool plain() const { return R_ == 0 && window_ == 0 && !sink_; }      // the form the unbiased attention kernels serve
 
     WeightTable weight_specs() const override {
         WeightTable t;
         t["dq"].shape = {Rq_, hidden_};
         t["dq.norm"].shape = {Rq_};
         t["dq.norm"].init_ones = true;
-        t["uq"].shape = {static_cast<long long>(H_) * D_, Rq_};
+        t["uq"].shape = {static_cast<long long>(H_) * (D_ + R_), Rq_};
         if (own_) {
-            t["dkv"].shape = {Rkv_, hidden_};
+            t["dkv"].shape = {Rkv_ + R_, hidden_};
             t["dkv.norm"].shape = {Rkv_};
             t["dkv.norm"].init_ones = true;
         }
         t["uk"].shape = {static_cast<long long>(H_) * D_, Rkv_};
         t["uv"].shape = {static_cast<long long>(H_) * V_, Rkv_};
         t["o"].shape = {hidden_, static_cast<long long>(H_) * V_};
+        if (sink_) t["sink"].shape = {H_};
+        if (gate_) t["g"].shape = {static_cast<long long>(H_) * V_, hidden_};
         return t;
     }
 
     void bind(const Weights& w, BindContext& bc) override {
-        if (own_) down_.bind({&w.at("dq"), &w.at("dkv")}, bc);
-        else down_.bind({&w.at("dq")}, bc);
+        std::vector<const HostTensor*> down{&w.at("dq")};      // one product for everything that reads the layer's input
+        if (own_) down.push_back(&w.at("dkv"));
+        if (gate_) down.push_back(&w.at("g"));
+        down_.bind(down, bc);
+        if (sink_) sinks_ = bc.upload(w.at("sink"), DType::F32);
+        rotary_ = position_->tables(bc);
+        if (R_ > 0 && (!rotary_.inv_freq || rotary_.rotary_dim > R_)) throw ConfigError("part 'latent_attention': rot_dim needs a rotary position part of at most that size");
         q_norm_ = bc.upload(w.at("dq.norm"), DType::F32);
         if (own_) kv_norm_ = bc.upload(w.at("dkv.norm"), DType::F32);
         up_q_.bind({&w.at("uq")}, bc);
@@ -53,16 +80,19 @@ public:
         out_.bind({&w.at("o")}, bc);
     }
 
-    bool graph_safe() const override { return true; }
+    bool graph_safe() const override { return position_->graph_safe(); }
 
     CacheNeed cache_need() const override {
         CacheNeed n;
-        n.kind = CacheNeed::All;
+        n.kind = window_ > 0 ? CacheNeed::Window : CacheNeed::All;
         n.kv_heads = 1;
-        n.key_dim = Rkv_;
+        n.key_dim = Rkv_ + R_;                             // the latent and, behind it, the rotated key part
         n.value_dim = 0;                                   // the latent is key and value at once
+        n.window = window_;
         return n;
     }
+    int down_cols() const { return Rq_ + (own_ ? Rkv_ + R_ : 0) + (gate_ ? H_ * V_ : 0); }
+    int gate_col() const { return Rq_ + (own_ ? Rkv_ + R_ : 0); }
 
     // Few tokens (decode steps) in bfloat16: the weight-streaming products of this library, with the layer's norm taken into
     // the down-projection and the residual sum into the output projection.
@@ -75,9 +105,15 @@ public:
     bool can_fuse(const StepContext& ctx, const Norm& norm) const override {
         const float* nw;
         float eps;
-        if (!norm.as_rms(&nw, &eps) || ctx.act_dtype != DType::BF16 || ctx.T_cap > max_rows()) return false;
+        if (!norm.as_rms(&nw, &eps) || !skinny(ctx)) return false;
+        return true;
+    }
+
+    // few tokens in bfloat16: the weight-streaming products take the layer's three projections
+    bool skinny(const StepContext& ctx) const {
+        if (ctx.act_dtype != DType::BF16 || ctx.T_cap > max_rows()) return false;
         if (down_.weight.dtype != DType::BF16 || up_q_.weight.dtype != DType::BF16 || out_.weight.dtype != DType::BF16) return false;
-        return hidden_ % 32 == 0 && Rq_ % 32 == 0 && (H_ * V_) % 32 == 0 && (Rq_ + (own_ ? Rkv_ : 0)) % 8 == 0 && (H_ * D_) % 8 == 0 && hidden_ % 8 == 0;
+        return hidden_ % 32 == 0 && Rq_ % 32 == 0 && (H_ * V_) % 32 == 0 && down_cols() % 8 == 0 && (H_ * (D_ + R_)) % 8 == 0 && hidden_ % 8 == 0;
     }
 
     void forward_fused(StepContext& ctx, float* h, Norm& norm) override {
@@ -86,32 +122,57 @@ public:
         norm.as_rms(&nw, &eps);
         KVView kv = ctx.kv();
         if (kv.owns != own_) throw ConfigError("a latent-attention layer and its schedule disagree about whose latents it reads");
-        const int down_cols = Rq_ + (own_ ? Rkv_ : 0);
-        float* down = static_cast<float*>(ctx.take_tokens(down_cols, DType::F32));
-        ops::skinny_linear(h, nw, eps, down_.weight, ctx.T, down, down_cols, true, nullptr, ctx.err, ctx.stream);
-        void* cq = ctx.take_tokens(Rq_, DType::BF16);
-        ops::latent_norm_write(down, down_cols, Rq_, Rkv_, static_cast<const float*>(q_norm_.ptr), own_ ? static_cast<const float*>(kv_norm_.ptr) : nullptr,
-                               eps_, cq, ctx, kv, own_);
-        ctx.give(down);
-        void* q = ctx.take_tokens(static_cast<long long>(H_) * D_, DType::BF16);
-        ops::skinny_linear(cq, nullptr, 0.f, up_q_.weight, ctx.T, q, H_ * D_, false, nullptr, ctx.err, ctx.stream);
-        ctx.give(cq);
-        void* o = attend(ctx, q, kv);
+        void* o = heads(ctx, h, nw, eps, kv, true);
         ops::skinny_linear(o, nullptr, 0.f, out_.weight, ctx.T, nullptr, hidden_, false, h, ctx.err, ctx.stream);
         ctx.give(o);
     }
 
-    // q [T, H*D] -> o [T, H*V] (a buffer the caller gives back); q is given back here
+    // x [T, hidden] (or, with norm_w, the float32 stream whose rows the first product norms) -> the heads' gated outputs [T, H*V]
+    void* heads(StepContext& ctx, const void* x, const float* norm_w, float eps, KVView kv, bool skinny_products) {
+        const DType act = ctx.act_dtype;
+        const int cols = down_cols();
+        float* down = static_cast<float*>(ctx.take_tokens(cols, DType::F32));
+        if (skinny_products) ops::skinny_linear(x, norm_w, eps, down_.weight, ctx.T, down, cols, true, nullptr, ctx.err, ctx.stream);
+        else down_.apply(ctx, x, act, down, DType::F32, ctx.T, ctx.T_cap);
+        void* cq = ctx.take_tokens(Rq_, act);
+        ops::latent_rope_norm_write(down, cols, Rq_, Rkv_, static_cast<const float*>(q_norm_.ptr), own_ ? static_cast<const float*>(kv_norm_.ptr) : nullptr,
+                                    eps_, cq, ctx, kv, own_, R_, rotary_);
+        if (!gate_) {                                      // (nothing else reads the projections' float32 result)
+            ctx.give(down);
+            down = nullptr;
+        }
+        const long long q_cols = static_cast<long long>(H_) * (D_ + R_);
+        void* q = ctx.take_tokens(q_cols, act);
+        if (skinny_products) ops::skinny_linear(cq, nullptr, 0.f, up_q_.weight, ctx.T, q, static_cast<int>(q_cols), false, nullptr, ctx.err, ctx.stream);
+        else up_q_.apply(ctx, cq, act, q, act, ctx.T, ctx.T_cap);
+        ctx.give(cq);
+        void* o = attend(ctx, q, kv);
+        if (gate_) ops::sigmoid_gate(o, down + gate_col(), cols, ctx.T, H_ * V_, act, ctx.stream);
+        ctx.give(down);
+        return o;
+    }
+
+    // q [T, H*(D+R)] -> o [T, H*V] (a buffer the caller gives back); q is given back here
     void* attend(StepContext& ctx, void* q, KVView kv) {
         const DType act = ctx.act_dtype;
-        // the key up-projection on the query's side: qa_h = W_uk,h^T q_h
-        void* qa = ctx.take_tokens(static_cast<long long>(H_) * Rkv_, act);
-        ops::linear_batched(q, static_cast<long long>(H_) * D_, D_, up_k_.ptr, static_cast<long long>(D_) * Rkv_, /*w_is_k_by_n=*/true, qa,
-                            static_cast<long long>(H_) * Rkv_, Rkv_, act, ctx.T, Rkv_, D_, H_, ctx.stream);
+        // the key up-projection on the query's side: qa_h = [W_uk,h^T q_h | turned q_rot,h]
+        const int Dk = Rkv_ + R_, Dq = D_ + R_;
+        void* qa = ctx.take_tokens(static_cast<long long>(H_) * Dk, act);
+        ops::linear_batched(q, static_cast<long long>(H_) * Dq, Dq, up_k_.ptr, static_cast<long long>(D_) * Rkv_, /*w_is_k_by_n=*/true, qa,
+                            static_cast<long long>(H_) * Dk, Dk, act, ctx.T, Rkv_, D_, H_, ctx.stream);
+        if (R_ > 0) ops::rotate_slice(q, static_cast<long long>(H_) * Dq, Dq, D_, qa, static_cast<long long>(H_) * Dk, Dk, Rkv_, rotary_, R_, H_, ctx);
         ctx.give(q);
         void* att = ctx.take_tokens(static_cast<long long>(H_) * Rkv_, act);
         kv.v_pages = kv.k_pages;
-        ops::attention(ctx, qa, H_ * Rkv_, kv, att, H_, 1, Rkv_, scale_, 0);
+        if (plain()) {
+            ops::attention(ctx, qa, H_ * Rkv_, kv, att, H_, 1, Rkv_, scale_, 0);
+        } else {
+            ops::BiasedMask mask;                          // no bias table: the mask, the sink, and values that are the front of the key rows
+            mask.window = window_;
+            mask.sink = sink_ ? static_cast<const float*>(sinks_.ptr) : nullptr;
+            mask.v_row_stride = Dk;
+            ops::attention_biased(ctx, qa, H_ * Dk, kv, att, H_, 1, Dk, Rkv_, scale_, mask);
+        }
         ctx.give(qa);
         // the value up-projection on the output's side: o_h = W_uv,h (sum_j p_j c_j)
         void* o = ctx.take_tokens(static_cast<long long>(H_) * V_, act);
@@ -127,36 +188,36 @@ public:
         if (kv.owns != own_)
             throw ConfigError(own_ ? "a latent-attention layer with a down-projection of its own was scheduled onto another run's cache"
                                    : "a latent-attention layer without a down-projection must read another run's cache");
-        const long long down_cols = Rq_ + (own_ ? Rkv_ : 0);
-        float* down = static_cast<float*>(ctx.take_tokens(down_cols, DType::F32));
-        down_.apply(ctx, x, act, down, DType::F32, ctx.T, ctx.T_cap);
-        void* cq = ctx.take_tokens(Rq_, act);
-        ops::latent_norm_write(down, static_cast<int>(down_cols), Rq_, Rkv_, static_cast<const float*>(q_norm_.ptr),
-                               own_ ? static_cast<const float*>(kv_norm_.ptr) : nullptr, eps_, cq, ctx, kv, own_);
-        ctx.give(down);
-        void* q = ctx.take_tokens(static_cast<long long>(H_) * D_, act);
-        up_q_.apply(ctx, cq, act, q, act, ctx.T, ctx.T_cap);
-        ctx.give(cq);
-        void* o = attend(ctx, q, kv);
-        out_.apply(ctx, o, act, out, act, ctx.T, ctx.T_cap);
+        const bool few = skinny(ctx);                      // (a choice by the step's capacity bucket)
+        void* o = heads(ctx, x, nullptr, 0.f, kv, few);
+        if (few) ops::skinny_linear(o, nullptr, 0.f, out_.weight, ctx.T, out, hidden_, false, nullptr, ctx.err, ctx.stream);
+        else out_.apply(ctx, o, act, out, act, ctx.T, ctx.T_cap);
         ctx.give(o);
     }
 
 private:
-    int hidden_, H_, D_, V_, Rq_, Rkv_;
-    bool own_;
+    int hidden_, H_, D_, V_, Rq_, Rkv_, R_, window_;
+    bool own_, sink_, gate_;
     float scale_, eps_;
+    std::shared_ptr<Position> position_;
+    RotaryTable rotary_;
     Linear down_, up_q_, out_;
-    DeviceTensor q_norm_, kv_norm_, up_k_, up_v_;
+    DeviceTensor q_norm_, kv_norm_, up_k_, up_v_, sinks_;
 };
 
 namespace {
 RegisterPart reg("mixer", "latent_attention", [](const json::Value& a) {
     const char* k = "latent_attention";
+    LatentAttention::Options o;
+    o.rot_dim = static_cast<int>(arg_int_or(a, "rot_dim", 0, k));
+    o.window = static_cast<int>(arg_int_or(a, "window", 0, k));
+    o.sink = arg_int_or(a, "sink", 0, k) != 0;
+    o.gate = arg_int_or(a, "gate", 0, k) != 0;
+    if (const json::Value* pos = a.find("position")) o.position = part_spec_from_json(*pos, "latent_attention.position");
     return std::make_shared<LatentAttention>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "heads", k)),
                                              static_cast<int>(arg_int(a, "dim", k)), static_cast<int>(arg_int(a, "vdim", k)),
                                              static_cast<int>(arg_int(a, "q_rank", k)), static_cast<int>(arg_int(a, "kv_rank", k)),
-                                             arg_number_or(a, "scale", 0.0, k), arg_number(a, "eps", k), arg_int_or(a, "own_latent", 1, k) != 0);
+                                             arg_number_or(a, "scale", 0.0, k), arg_number(a, "eps", k), arg_int_or(a, "own_latent", 1, k) != 0, o);
 });
 }  // namespace
 

@@ -12,6 +12,11 @@
 // best of `groups` equal groups of neighbours (a group's score is its largest choice score); the weights are s * `scale`, not
 // renormalised.  The last `identity` outputs of the router are identity experts without tensors: their result is the input.
 // A second form of expert (`glu` = 1): gate and up matrices, min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u, +-limit) + 1).
+//
+// A third form of routing (`routing` = "sigmoid"): s = sigmoid(z), every output scored alone; the `top` largest are chosen and their
+// scores are the weights, not renormalised; there is no correction tensor unless `correction` = 1.  A third form of expert (`glu` = 2):
+// W_down (silu(W_gate h) * (W_up h)) where the routing weight multiplies the expert's INPUT, h = w x, not its output; the shared expert
+// (tensors shared.gate, shared.up, shared.down) has the same form and runs with w = 1, without a gate of its own.
 #include "args.h"
 #include "linear.h"
 
@@ -29,8 +34,10 @@ struct Routing {
     bool scored = false;                 // false: softmax over the chosen logits; true: the form described above
     int groups = 1, groups_keep = 1, identity = 0;
     float scale = 1.f;
-    bool glu = false;
+    int glu = VM_GLU_NONE;               // VM_GLU_*
     float limit = 0.f, alpha = 1.702f;
+    int score_kind = VM_SCORE_SOFTMAX;   // of the scored form
+    bool correction = true;              // the scored form has a correction tensor
 };
 
 class RoutedExperts : public FeedForward {
@@ -45,7 +52,8 @@ public:
             throw ConfigError(format("part '%s': %d groups (of which %d stay) must divide the router's %d outputs", k, r.groups, r.groups_keep, outputs));
         const int eligible = outputs / r.groups * r.groups_keep;
         if (top < 1 || top > eligible) throw ConfigError(format("part '%s': top (%d) must be within 1..%d, the outputs that can be chosen", k, top, eligible));
-        if (r.glu && !(r.limit > 0)) throw ConfigError(format("part '%s': gated experts need a positive limit", k));
+        if (r.glu == VM_GLU_CLAMPED && !(r.limit > 0)) throw ConfigError(format("part '%s': gated experts need a positive limit", k));
+        if (r.glu == VM_GLU_SILU_WEIGHTED_INPUT && (r.identity > 0 || gate_)) throw ConfigError(format("part '%s': experts with the weight on their input have neither identity experts nor a gated shared expert", k));
     }
 
     ops::ExpertKind kind() const {
@@ -59,18 +67,23 @@ public:
         return k;
     }
     bool general() const { return r_.scored || r_.glu; }      // the steps that take the general kernels
+    bool shared_glu() const { return r_.glu == VM_GLU_SILU_WEIGHTED_INPUT; }      // the shared expert has a gate matrix too
 
     WeightTable weight_specs() const override {
         WeightTable t;
         t["router"].shape = {E_ + r_.identity, hidden_};
-        if (r_.scored) t["correction"].shape = {E_ + r_.identity};
-        else t["router.b"].shape = {E_};
+        if (r_.scored) {
+            if (r_.correction) t["correction"].shape = {E_ + r_.identity};
+        } else {
+            t["router.b"].shape = {E_};
+        }
         for (int e = 0; e < E_; ++e) {
             if (r_.glu) t[format("e%d.gate", e)].shape = {ff_, hidden_};
             t[format("e%d.up", e)].shape = {ff_, hidden_};
             t[format("e%d.down", e)].shape = {hidden_, ff_};
         }
         if (sff_ > 0) {
+            if (shared_glu()) t["shared.gate"].shape = {sff_, hidden_};
             t["shared.up"].shape = {sff_, hidden_};
             t["shared.down"].shape = {hidden_, sff_};
             if (gate_) t["shared.sg"].shape = {1, hidden_};
@@ -80,7 +93,7 @@ public:
 
     void bind(const Weights& w, BindContext& bc) override {
         router_ = bc.upload(w.at("router"), DType::F32);
-        router_b_ = bc.upload(w.at(r_.scored ? "correction" : "router.b"), DType::F32);
+        if (!r_.scored || r_.correction) router_b_ = bc.upload(w.at(r_.scored ? "correction" : "router.b"), DType::F32);
         std::vector<const HostTensor*> ups, downs, all;
         for (int e = 0; e < E_; ++e) {
             if (r_.glu) ups.push_back(&w.at(format("e%d.gate", e)));      // an expert's gate rows lie before its up rows
@@ -90,6 +103,7 @@ public:
         all = ups;
         all.insert(all.end(), downs.begin(), downs.end());
         if (sff_ > 0) {
+            if (shared_glu()) all.push_back(&w.at("shared.gate"));
             all.push_back(&w.at("shared.up"));
             all.push_back(&w.at("shared.down"));
         }
@@ -97,7 +111,8 @@ public:
         up_ = bc.upload_stacked(ups, kept);
         down_ = bc.upload_stacked(downs, kept);
         if (sff_ > 0) {
-            s_up_ = bc.upload(w.at("shared.up"), kept);
+            if (shared_glu()) s_up_ = bc.upload_stacked({&w.at("shared.gate"), &w.at("shared.up")}, kept);      // gate rows before up rows
+            else s_up_ = bc.upload(w.at("shared.up"), kept);
             s_down_ = bc.upload(w.at("shared.down"), kept);
             if (gate_) s_gate_ = bc.upload(w.at("shared.sg"), DType::F32);
         }
@@ -130,8 +145,9 @@ public:
     void route(StepContext& ctx, const void* x, const float* nw, float eps, int* chosen, float* weight, float* sgate) {
         if (r_.scored) {
             if (gate_) throw Error("routed_experts: the scored router has no gate for a shared expert");
-            ops::expert_router_scored(x, nw, eps, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr), ctx.T, hidden_,
-                                      E_ + r_.identity, top_, r_.groups, r_.groups_keep, r_.scale, chosen, weight, ctx.act_dtype, ctx.stream);
+            ops::expert_router_scored(x, nw, eps, static_cast<const float*>(router_.ptr), r_.correction ? static_cast<const float*>(router_b_.ptr) : nullptr,
+                                      ctx.T, hidden_, E_ + r_.identity, top_, r_.groups, r_.groups_keep, r_.scale, r_.score_kind, chosen, weight,
+                                      ctx.act_dtype, ctx.stream);
             return;
         }
         ops::expert_router(x, nw, eps, static_cast<const float*>(router_.ptr), static_cast<const float*>(router_b_.ptr),
@@ -173,8 +189,15 @@ public:
             float* shared_y = nullptr;
             if (sff_ > 0) {
                 void* u = ctx.take_tokens(sff_, DType::BF16);
-                ops::linear(x, DType::BF16, hidden_, s_up_, u, DType::BF16, ctx.T, ctx.stream);
-                ops::activation(u, u, static_cast<long long>(ctx.T) * sff_, sact_, DType::BF16, ctx.stream);
+                if (shared_glu()) {
+                    void* gu = ctx.take_tokens(2ll * sff_, DType::BF16);
+                    ops::linear(x, DType::BF16, hidden_, s_up_, gu, DType::BF16, ctx.T, ctx.stream);
+                    ops::gated_activation(gu, u, ctx.T, sff_, VM_ACT_SILU, DType::BF16, ctx.stream);
+                    ctx.give(gu);
+                } else {
+                    ops::linear(x, DType::BF16, hidden_, s_up_, u, DType::BF16, ctx.T, ctx.stream);
+                    ops::activation(u, u, static_cast<long long>(ctx.T) * sff_, sact_, DType::BF16, ctx.stream);
+                }
                 shared_y = static_cast<float*>(ctx.take_tokens(hidden_, DType::F32));
                 ops::linear(u, DType::BF16, sff_, s_down_, shared_y, DType::F32, ctx.T, ctx.stream);
                 ctx.give(u);
@@ -232,13 +255,17 @@ RegisterPart reg("feed_forward", "routed_experts", [](const json::Value& a) {
     const std::string act = arg_string_or(a, "activation", "relu_squared", k);
     Routing r;
     const std::string routing = arg_string_or(a, "routing", "chosen_softmax", k);
-    if (routing != "chosen_softmax" && routing != "scored") throw ConfigError("part 'routed_experts': routing is \"chosen_softmax\" or \"scored\"");
-    r.scored = routing == "scored";
+    if (routing != "chosen_softmax" && routing != "scored" && routing != "sigmoid")
+        throw ConfigError("part 'routed_experts': routing is \"chosen_softmax\", \"scored\" or \"sigmoid\"");
+    r.scored = routing != "chosen_softmax";
+    r.score_kind = routing == "sigmoid" ? VM_SCORE_SIGMOID : VM_SCORE_SOFTMAX;
+    r.correction = arg_int_or(a, "correction", routing == "scored" ? 1 : 0, k) != 0;
     r.groups = static_cast<int>(arg_int_or(a, "groups", 1, k));
     r.groups_keep = static_cast<int>(arg_int_or(a, "groups_keep", r.groups, k));
     r.identity = static_cast<int>(arg_int_or(a, "identity", 0, k));
     r.scale = static_cast<float>(arg_number_or(a, "scale", 1.0, k));
-    r.glu = arg_int_or(a, "glu", 0, k) != 0;
+    r.glu = static_cast<int>(arg_int_or(a, "glu", 0, k));
+    if (r.glu < VM_GLU_NONE || r.glu > VM_GLU_SILU_WEIGHTED_INPUT) throw ConfigError("part 'routed_experts': glu is 0 (none), 1 (clamped) or 2 (SiLU, weight on the input)");
     r.limit = static_cast<float>(arg_number_or(a, "limit", 0.0, k));
     r.alpha = static_cast<float>(arg_number_or(a, "alpha", 1.702, k));
     return std::make_shared<RoutedExperts>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "experts", k)),
