@@ -295,6 +295,32 @@ def semesun_config(z, x):
                        {"type": "mamba2", "mixer": ssm, "mlp": moe}]}
 
 
+# ------------------------------------------------------------------------------------------------ --design fidizen
+# The same widths, four layers of latent attention with a rotated shared key part of 32 values, a window of 1,024, a sink and an output
+# gate, behind a convolution of four taps, alternately with the polynomial feed-forward and with routed experts (sigmoid scores, SiLU-gated
+# experts, a shared expert); beside it Kogilix with four layers of its latent attention (the closest design of this library: the same
+# ranks and heads, no rotation, window, sink or gate; dense gated unit / routed experts) and the Llama decoder at equal width and depth.
+FIDIZEN_EXTRA = {"w1024": dict(rot_dim=32, window=1024, taps=4, base=10000.0), "w2048": dict(rot_dim=32, window=1024, taps=4, base=10000.0)}
+
+
+def fidizen_config(z, x):
+    att = {"heads": z["heads"], "dim": z["dim"], "rot_dim": x["rot_dim"], "vdim": z["dim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"],
+           "scale": (z["dim"] + x["rot_dim"]) ** -0.5, "rot": {"base": x["base"], "dims": x["rot_dim"]}, "mask": {"size": x["window"]}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared_ff"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    return {"architecture": "Fidizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": z["width"] ** 0.5},
+            "canon": {"taps": x["taps"]},
+            "layers": [{"type": "latent_attention", "mixer": att, "mlp": mlp} for mlp in (dense, moe, dense, moe)]}
+
+
+def kogilix_attention_config(z):
+    att = {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"], "scale": z["dim"] ** -0.5}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared_ff"]}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    return {"architecture": "Kogilix", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": [{"type": "latent_attention", "mixer": att, "mlp": mlp} for mlp in (dense, moe, dense, moe)]}
+
+
 def llama_config_like(z):
     return {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "num_hidden_layers": 4, "hidden_size": z["width"],
             "num_attention_heads": z["heads"], "num_key_value_heads": z["heads"], "intermediate_size": z["ff"], "vocab_size": z["vocab"],
@@ -315,7 +341,7 @@ def op_table(vm, engine, entries):
 
 
 def design_arm(args):
-    """Prompt and decode throughput of a design (Kogilix, Semesun) at a few sizes, beside the library's other models at equal size."""
+    """Prompt and decode throughput of a design (Kogilix, Semesun, Fidizen) at a few sizes, beside the library's other models at equal size."""
     import numpy as np
     import velomind_b200 as vm
     T, B, prompt_len = 2048, 8, 512
@@ -328,6 +354,8 @@ def design_arm(args):
         models = [("kogilix", kogilix_config(z)), ("llama", llama_config_like(z))]
         if args.design == "semesun":
             models.insert(0, ("semesun", semesun_config(z, SEMESUN_EXTRA[name])))
+        if args.design == "fidizen":
+            models = [("fidizen", fidizen_config(z, FIDIZEN_EXTRA[name])), ("kogilix_attention", kogilix_attention_config(z)), ("llama", llama_config_like(z))]
         for which, cfg in models:
             with tempfile.TemporaryDirectory(prefix="velomind_bench_") as folder:
                 vm.write_random_model(folder, cfg, seed=0, std=0.02)
@@ -456,7 +484,7 @@ def main() -> int:
     ap.add_argument("--quick", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="sizes of the random model: the benchmark's SmolLM2-135M (default), or the 360M / 1.7B shapes of the family")
-    ap.add_argument("--design", default="", choices=["", "kogilix", "semesun"],
+    ap.add_argument("--design", default="", choices=["", "kogilix", "semesun", "fidizen"],
                     help="instead of the benchmark: prompt and decode throughput of another design of the library at a few layer sizes, "
                          "beside the Llama decoder at equal size (one JSON line of its own)")
     args = ap.parse_args()

@@ -366,8 +366,8 @@ ModelPlan windowed_plan(const json::Value& data, const std::string& where) {
     return plan;
 }
 
-// whatever config.json names: "embedding", "final_norm", "head" as parts, "blocks": [{arrangement, mixer, feed_forward, mixer_norm,
-// feed_forward_norm}], "hidden", "vocab", "limit"
+// whatever config.json names: "embedding", "final_norm", "head" as parts, "blocks": [{arrangement, arrangement_args, mixer, feed_forward,
+// mixer_norm, feed_forward_norm}], "hidden", "vocab", "limit"
 ModelPlan probe_plan(const json::Value& data, const std::string& where) {
     KeyReader r(data, where);
     ModelPlan plan;
@@ -390,6 +390,7 @@ ModelPlan probe_plan(const json::Value& data, const std::string& where) {
         for (const auto& b : blocks->as_array()) {
             BlockSpec spec;
             spec.arrangement = b.find("arrangement")->as_string();
+            if (const json::Value* a = b.find("arrangement_args")) spec.arrangement_args = *a;
             spec.prefix = format("layers.%d.", l);
             spec.mixer = part(b, "mixer");
             spec.feed_forward = part(b, "feed_forward");

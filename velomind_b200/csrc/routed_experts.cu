@@ -213,10 +213,12 @@ __global__ void router_scored_kernel(const void* __restrict__ x, const float* __
     __syncthreads();
     if (warp != 0) return;
     if (score_kind == VM_SCORE_SIGMOID) {                 // every output scored alone: s = 1 / (1 + exp(-z))
+        // Without a correction the order of the scores is the order of the logits, and the logits still tell apart what the sigmoid
+        // rounds to the same number (every z above 17 gives 1.0f): the choice is made on z.
         for (int e = lane; e < n_out; e += 32) {
-            const float p = 1.0f / (1.0f + expf(-sc[e]));
+            const float z = sc[e], p = 1.0f / (1.0f + expf(-z));
             sc[e] = p;
-            ch[e] = p + (correction ? correction[e] : 0.f);
+            ch[e] = correction ? p + correction[e] : z;
         }
     } else {
         float mx = -INFINITY;

@@ -103,6 +103,42 @@ __global__ void norm_residual_kernel(float* __restrict__ h, const Y* __restrict_
     for (int i = threadIdx.x; i < hid; i += blockDim.x) h[(size_t)t * hid + i] += row[i] * inv * w[i];
 }
 
+// The same sum for steps of one token per sequence, followed by the NEXT sublayer's input convolution on the row just made (a thread owns
+// its channels through both): h += rmsnorm(y) * w ; out = h + conv(h) with the kept inputs moved on.  grid (B).
+template <typename Y, typename T>
+__global__ void norm_residual_conv_step_kernel(float* __restrict__ h, const Y* __restrict__ y, long long ld, const float* __restrict__ w, int hid, float eps,
+                                               const float* __restrict__ taps, float* __restrict__ state, long long state_stride, int state_offset,
+                                               const int* __restrict__ slots, T* __restrict__ out, int K) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int t = blockIdx.x;
+    const Y* yr = y + (size_t)t * ld;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hid; i += blockDim.x) {
+        const float v = vm_to_float(yr[i]);
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = vm_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
+    float* kept = state + (size_t)slots[t] * state_stride + state_offset;
+    for (int c = threadIdx.x; c < hid; c += blockDim.x) {
+        const float x = h[(size_t)t * hid + c] + row[c] * inv * w[c];
+        h[(size_t)t * hid + c] = x;
+        const float* tw = taps + (size_t)c * K;
+        float acc = x * (1.0f + tw[K - 1]);
+        for (int j = 0; j < K - 1; ++j) {
+            const float v = kept[(size_t)j * hid + c];
+            acc = fmaf(tw[j], v, acc);
+            if (j > 0) kept[(size_t)(j - 1) * hid + c] = v;
+        }
+        if (K > 1) kept[(size_t)(K - 2) * hid + c] = x;
+        out[(size_t)t * hid + c] = vm_from_float<T>(acc);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ polynomial activation with unit-rms powers
 // one block per token; z [T, n] in Z (float32 or the activation dtype), out in T
 template <typename Z, typename T>
@@ -219,6 +255,30 @@ VM_API int vm_norm_residual_add(float* h, const void* y, long long ld, int y_dty
     if (y_dtype == VM_F32) vm_launch_pdl(norm_residual_kernel<float>, dim3(T), dim3(threads), smem, stream, h, (const float*)y, ld, w, hid, eps);
     else if (y_dtype == VM_BF16)
         vm_launch_pdl(norm_residual_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, h, (const __nv_bfloat16*)y, ld, w, hid, eps);
+    else return VM_ERR_UNSUPPORTED;
+    return vm_launch_status();
+}
+
+// One token per sequence (token s is sequence s's): h += rmsnorm(y) * w, then out = h + conv(h) as vm_input_conv does for such a step,
+// the kept inputs at state_offset moved on.  y and out in act_dtype (y_dtype VM_F32: y float32).
+VM_API int vm_norm_residual_conv_step(float* h, const void* y, long long ld, int y_dtype, const float* w, int B, int hid, float eps, const float* taps,
+                                      float* state, long long state_stride, int state_offset, const int* slots, void* out, int K, int act_dtype,
+                                      cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (hid <= 0 || ld < hid || K < 1 || K > 64 || (K > 1 && (!state || state_offset < 0 || state_offset + (long long)(K - 1) * hid > state_stride)))
+        return VM_ERR_BAD_ARG;
+    const int threads = hid >= 512 ? 256 : 128;
+    const size_t smem = (size_t)hid * sizeof(float);
+    if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    if (y_dtype == VM_F32 && act_dtype == VM_F32)
+        vm_launch_pdl(norm_residual_conv_step_kernel<float, float>, dim3(B), dim3(threads), smem, stream, h, (const float*)y, ld, w, hid, eps, taps, state,
+                      state_stride, state_offset, slots, (float*)out, K);
+    else if (y_dtype == VM_F32 && act_dtype == VM_BF16)
+        vm_launch_pdl(norm_residual_conv_step_kernel<float, __nv_bfloat16>, dim3(B), dim3(threads), smem, stream, h, (const float*)y, ld, w, hid, eps, taps,
+                      state, state_stride, state_offset, slots, (__nv_bfloat16*)out, K);
+    else if (y_dtype == VM_BF16 && act_dtype == VM_BF16)
+        vm_launch_pdl(norm_residual_conv_step_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(B), dim3(threads), smem, stream, h, (const __nv_bfloat16*)y, ld, w,
+                      hid, eps, taps, state, state_stride, state_offset, slots, (__nv_bfloat16*)out, K);
     else return VM_ERR_UNSUPPORTED;
     return vm_launch_status();
 }

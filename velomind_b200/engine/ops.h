@@ -76,6 +76,17 @@ inline void norm_residual_add(float* h, const void* y, long long ld, DType y_dty
     check(vm_norm_residual_add(h, y, ld, code(y_dtype), w, T, hid, eps, s), "norm_residual_add", s);
 }
 
+// a step of one token per sequence: that sum and the next sublayer's input convolution in one launch
+inline void norm_residual_conv_step(float* h, const void* y, DType y_dtype, const float* w, float eps, const float* taps, int K, int state_offset,
+                                    StepContext& ctx, void* out) {
+    Timed t("norm_residual_conv_step", ctx.stream);
+    if (K > 1 && (!ctx.state() || ctx.state_floats() < state_offset + (K - 1) * ctx.hidden))
+        throw CacheError("input convolution: the cache holds no state area for this layer's kept inputs");
+    check(vm_norm_residual_conv_step(h, y, ctx.hidden, code(y_dtype), w, ctx.B, ctx.hidden, eps, taps, ctx.state(), ctx.state_floats(), state_offset, ctx.slots,
+                                     out, K, code(ctx.act_dtype), ctx.stream),
+          "norm_residual_conv_step", ctx.stream);
+}
+
 inline void polynorm(const void* z, DType z_dtype, const float* coef, void* out, int T, int n, float eps, DType act, cudaStream_t s) {
     Timed t("polynorm", s);
     check(vm_polynorm(z, code(z_dtype), coef, out, T, n, eps, code(act), s), "polynorm", s);

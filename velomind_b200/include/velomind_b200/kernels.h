@@ -69,6 +69,10 @@ int vm_input_conv(const float* h, const float* taps, float* state, long long sta
                   const int* seq_of_token, const int* cu_tokens, const int* slots, void* out, int T, int B, int hid, int K, int one_token_each,
                   int act_dtype, cudaStream_t stream);
 int vm_norm_residual_add(float* h, const void* y, long long ld, int y_dtype, const float* w, int T, int hid, float eps, cudaStream_t stream);
+// one token per sequence: the same sum, then out = h + conv(h) of the next sublayer on the row just made, its kept inputs moved on
+int vm_norm_residual_conv_step(float* h, const void* y, long long ld, int y_dtype, const float* w, int B, int hid, float eps, const float* taps,
+                               float* state, long long state_stride, int state_offset, const int* slots, void* out, int K, int act_dtype,
+                               cudaStream_t stream);
 // a N(z) + b N(z^2) + c N(z^3) + e per token, N: division by the root mean square over the token's n values; coef float32 [4]
 int vm_polynorm(const void* z, int z_dtype, const float* coef, void* out, int T, int n, float eps, int act_dtype, cudaStream_t stream);
 int vm_rotate_slice(const void* src, long long src_ld, int src_head, int src_off, void* dst, long long dst_ld, int dst_head, int dst_off,

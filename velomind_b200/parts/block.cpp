@@ -95,25 +95,51 @@ public:
             ctx.give(pending);
         }
         const int base = p_.mixer->cache_need().state_floats;
-        half(ctx, h, taps_mixer_, base, *p_.mixer_norm, [&](const void* x, void* y) { p_.mixer->forward(ctx, x, y); });
-        if (feed_forward_)
-            half(ctx, h, taps_ff_, base + (K_ - 1) * hidden_, *p_.feed_forward_norm, [&](const void* x, void* y) { p_.feed_forward->forward(ctx, x, y); });
+        const Rms n1 = rms_of(*p_.mixer_norm);
+        const long long n = static_cast<long long>(ctx.T) * hidden_;
+        const bool copies = convolves() || ctx.act_dtype != DType::F32;      // (a float32 sublayer without a convolution reads the stream in place)
+        void* x = ctx.take_tokens(hidden_, ctx.act_dtype);
+        read_stream(ctx, h, taps_mixer_, base, x, n);
+        void* y = ctx.take_tokens(hidden_, ctx.act_dtype);
+        p_.mixer->forward(ctx, copies ? x : h, y);
+        ctx.give(x);
+        if (!feed_forward_) {
+            ops::norm_residual_add(h, y, hidden_, ctx.act_dtype, n1.weight, n1.eps, ctx.T, hidden_, ctx.stream);
+            ctx.give(y);
+            return nullptr;
+        }
+        const Rms n2 = rms_of(*p_.feed_forward_norm);
+        x = ctx.take_tokens(hidden_, ctx.act_dtype);
+        if (convolves() && ctx.one_token_each) {
+            // a decode step: the mixer's sum and the feed-forward's convolution on the row just made, one launch
+            ops::norm_residual_conv_step(h, y, ctx.act_dtype, n1.weight, n1.eps, static_cast<const float*>(taps_ff_.ptr), K_, base + (K_ - 1) * hidden_, ctx, x);
+        } else {
+            ops::norm_residual_add(h, y, hidden_, ctx.act_dtype, n1.weight, n1.eps, ctx.T, hidden_, ctx.stream);
+            read_stream(ctx, h, taps_ff_, base + (K_ - 1) * hidden_, x, n);
+        }
+        ctx.give(y);
+        y = ctx.take_tokens(hidden_, ctx.act_dtype);
+        p_.feed_forward->forward(ctx, copies ? x : h, y);
+        ctx.give(x);
+        ops::norm_residual_add(h, y, hidden_, ctx.act_dtype, n2.weight, n2.eps, ctx.T, hidden_, ctx.stream);
+        ctx.give(y);
         return nullptr;
     }
 
 private:
-    template <class Run> void half(StepContext& ctx, float* h, const DeviceTensor& taps, int state_offset, Norm& norm, Run run) {
-        const float* nw = nullptr;
+    struct Rms {
+        const float* weight = nullptr;
         float eps = 0.f;
-        if (!norm.as_rms(&nw, &eps)) throw ConfigError("arrangement 'output_norm': the norm on a sublayer's output must be a root-mean-square norm");
-        void* x = ctx.take_tokens(hidden_, ctx.act_dtype);
+    };
+    static Rms rms_of(Norm& norm) {
+        Rms r;
+        if (!norm.as_rms(&r.weight, &r.eps)) throw ConfigError("arrangement 'output_norm': the norm on a sublayer's output must be a root-mean-square norm");
+        return r;
+    }
+    // x = what a sublayer reads of the stream: h + conv(h), or h in the activation dtype
+    void read_stream(StepContext& ctx, const float* h, const DeviceTensor& taps, int state_offset, void* x, long long n) {
         if (convolves()) ops::input_conv(h, static_cast<const float*>(taps.ptr), K_, state_offset, ctx, x);
-        else if (ctx.act_dtype != DType::F32) ops::convert(h, DType::F32, x, ctx.act_dtype, static_cast<long long>(ctx.T) * hidden_, ctx.stream);
-        void* y = ctx.take_tokens(hidden_, ctx.act_dtype);
-        run(convolves() || ctx.act_dtype != DType::F32 ? x : h, y);      // (a float32 sublayer without a convolution reads the stream in place)
-        ctx.give(x);
-        ops::norm_residual_add(h, y, hidden_, ctx.act_dtype, nw, eps, ctx.T, hidden_, ctx.stream);
-        ctx.give(y);
+        else if (ctx.act_dtype != DType::F32) ops::convert(h, DType::F32, x, ctx.act_dtype, n, ctx.stream);
     }
     BlockParts p_;
     int hidden_, K_;
