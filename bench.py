@@ -548,7 +548,7 @@ def main() -> int:
         # end to end through the public entry point: host token ids in, host token ids out
         rng = np.random.default_rng(1)
         prompts = [rng.integers(0, vocab, prompt_len).tolist() for _ in range(B)]
-        # the host reads every step's tokens and sends the next step's descriptors (steps_per_sync=1), as the contract asks
+        # the host reads every step's tokens and sends the next step's descriptors (steps_per_sync=1): an end-to-end step includes both
         te.generate(prompts, temperature=0.0, max_tokens=warmup + 1, stop_tokens=(), steps_per_sync=1)
         # bytes are counted where they are copied (descriptors and sampler parameters up, sampled tokens down); what the
         # prompt step alone moves is taken off, as the timed region is the decode steps

@@ -9,6 +9,8 @@
 //   multiplication by the sigmoid of a gate.
 //
 // The residual stream is float32; everything here computes in float32 and rounds once on the way out.
+#include <cstdint>
+
 #include "common.cuh"
 
 namespace {
@@ -39,6 +41,62 @@ __global__ void input_conv_kernel(const float* __restrict__ h, const float* __re
         }
         out[(size_t)t * hid + c] = vm_from_float<T>(acc);
     }
+}
+
+// The same for bfloat16 outputs and hid % 4 == 0: a thread makes four neighbouring channels of one token with 16-byte loads (the rows of
+// earlier tokens come out of L1 / L2: the step's rows are read from memory once).  KT: the number of taps when it is 2, 3 or 4 (their
+// 4 x K weights are K 16-byte loads), 0: any number (scalar loads of the weights).
+template <int KT>
+__global__ void __launch_bounds__(256)
+input_conv_vec_kernel(const float* __restrict__ h, const float* __restrict__ taps, const float* __restrict__ state, long long state_stride,
+                      int state_offset, const int* __restrict__ seq_of_token, const int* __restrict__ cu_tokens, const int* __restrict__ slots,
+                      __nv_bfloat16* __restrict__ out, int hid, int K_any, long long n_vec) {
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_vec) return;
+    const int K = KT ? KT : K_any;
+    const int per = hid >> 2;
+    const int t = (int)(idx / per), c = (int)(idx - (long long)t * per) << 2;
+    const int seq = seq_of_token[t];
+    const int in_step = t - cu_tokens[seq];
+    const float* kept = state + (size_t)slots[seq] * state_stride + state_offset;
+    float tw[KT ? 4 * KT : 4];
+    if (KT) {
+        const float4* w4 = reinterpret_cast<const float4*>(taps + (size_t)c * K);
+#pragma unroll
+        for (int q = 0; q < (KT ? KT : 1); ++q) {
+            const float4 v = w4[q];
+            tw[4 * q] = v.x; tw[4 * q + 1] = v.y; tw[4 * q + 2] = v.z; tw[4 * q + 3] = v.w;
+        }
+    }
+    const float4 x = *reinterpret_cast<const float4*>(h + (size_t)t * hid + c);
+    float4 acc;
+    if (KT) {
+        acc.x = x.x * (1.0f + tw[0 * KT + KT - 1]); acc.y = x.y * (1.0f + tw[1 * KT + KT - 1]);
+        acc.z = x.z * (1.0f + tw[2 * KT + KT - 1]); acc.w = x.w * (1.0f + tw[3 * KT + KT - 1]);
+    } else {
+        acc.x = x.x * (1.0f + taps[(size_t)c * K + K - 1]); acc.y = x.y * (1.0f + taps[(size_t)(c + 1) * K + K - 1]);
+        acc.z = x.z * (1.0f + taps[(size_t)(c + 2) * K + K - 1]); acc.w = x.w * (1.0f + taps[(size_t)(c + 3) * K + K - 1]);
+    }
+#pragma unroll
+    for (int j = 0; j < (KT ? KT - 1 : 64); ++j) {
+        if (!KT && j >= K - 1) break;
+        const int back = K - 1 - j;
+        const float* src = back <= in_step ? h + (size_t)(t - back) * hid + c : kept + (size_t)(K - 1 - back + in_step) * hid + c;
+        const float4 v = *reinterpret_cast<const float4*>(src);
+        if (KT) {
+            acc.x = fmaf(tw[0 * KT + j], v.x, acc.x); acc.y = fmaf(tw[1 * KT + j], v.y, acc.y);
+            acc.z = fmaf(tw[2 * KT + j], v.z, acc.z); acc.w = fmaf(tw[3 * KT + j], v.w, acc.w);
+        } else {
+            acc.x = fmaf(taps[(size_t)c * K + j], v.x, acc.x); acc.y = fmaf(taps[(size_t)(c + 1) * K + j], v.y, acc.y);
+            acc.z = fmaf(taps[(size_t)(c + 2) * K + j], v.z, acc.z); acc.w = fmaf(taps[(size_t)(c + 3) * K + j], v.w, acc.w);
+        }
+    }
+    const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x, acc.y), o23 = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 o;
+    o.x = *reinterpret_cast<const unsigned*>(&o01); o.y = *reinterpret_cast<const unsigned*>(&o23);
+    *reinterpret_cast<uint2*>(out + (size_t)t * hid + c) = o;
 }
 
 // grid (B, ceil(hid / threads)); a thread owns one channel of one sequence and moves its K - 1 kept inputs on by the step's tokens.
@@ -101,6 +159,39 @@ __global__ void norm_residual_kernel(float* __restrict__ h, const Y* __restrict_
     ss = vm_block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
     for (int i = threadIdx.x; i < hid; i += blockDim.x) h[(size_t)t * hid + i] += row[i] * inv * w[i];
+}
+
+// The same for bfloat16 y with hid % 4 == 0 and ld % 4 == 0: a warp per token, 8-byte loads of y (its second pass finds the row in L1),
+// 16-byte updates of h; no block-wide barrier.
+constexpr int NR_WARPS = 4;
+__global__ void __launch_bounds__(NR_WARPS * 32)
+norm_residual_vec_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, long long ld, const float* __restrict__ w, int T, int hid, float eps) {
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int t = blockIdx.x * NR_WARPS + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const uint2* yr = reinterpret_cast<const uint2*>(y + (size_t)t * ld);
+    const int n4 = hid >> 2;
+    float ss = 0.f;
+    for (int i = lane; i < n4; i += 32) {
+        const uint2 d = yr[i];
+        const __nv_bfloat162 d01 = *reinterpret_cast<const __nv_bfloat162*>(&d.x), d23 = *reinterpret_cast<const __nv_bfloat162*>(&d.y);
+        const float a = __low2float(d01), b = __high2float(d01), c = __low2float(d23), e = __high2float(d23);
+        ss += a * a + b * b + c * c + e * e;
+    }
+    ss = vm_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
+    float4* hr = reinterpret_cast<float4*>(h + (size_t)t * hid);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    for (int i = lane; i < n4; i += 32) {
+        const uint2 d = yr[i];
+        const __nv_bfloat162 d01 = *reinterpret_cast<const __nv_bfloat162*>(&d.x), d23 = *reinterpret_cast<const __nv_bfloat162*>(&d.y);
+        const float4 ww = w4[i];
+        float4 v = hr[i];
+        v.x += __low2float(d01) * inv * ww.x; v.y += __high2float(d01) * inv * ww.y;
+        v.z += __low2float(d23) * inv * ww.z; v.w += __high2float(d23) * inv * ww.w;
+        hr[i] = v;
+    }
 }
 
 // The same sum for steps of one token per sequence, followed by the NEXT sublayer's input convolution on the row just made (a thread owns
@@ -166,6 +257,49 @@ __global__ void polynorm_kernel(const Z* z, const float* __restrict__ coef, T* o
     }
 }
 
+// The same in bfloat16 with n % 8 == 0: 16-byte loads and stores, the three sums reduced together.  (z may be out.)
+__global__ void __launch_bounds__(256) polynorm_vec_kernel(const __nv_bfloat16* z, const float* __restrict__ coef, __nv_bfloat16* out, int n, float eps) {
+    __shared__ float red[3][8];
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint4* zr = reinterpret_cast<const uint4*>(z + (size_t)t * n);
+    uint4* orow = reinterpret_cast<uint4*>(out + (size_t)t * n);
+    const int n8 = n >> 3;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < n8; i += 256) {
+        const uint4 d = zr[i];
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float a = __low2float(p[k]), b = __high2float(p[k]), a2 = a * a, b2 = b * b;
+            s2 += a2 + b2;
+            s4 += a2 * a2 + b2 * b2;
+            s6 += a2 * a2 * a2 + b2 * b2 * b2;
+        }
+    }
+    s2 = vm_warp_sum(s2); s4 = vm_warp_sum(s4); s6 = vm_warp_sum(s6);
+    if (lane == 0) { red[0][warp] = s2; red[1][warp] = s4; red[2][warp] = s6; }
+    __syncthreads();
+    s2 = s4 = s6 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { s2 += red[0][k]; s4 += red[1][k]; s6 += red[2][k]; }
+    const float a = coef[0] / sqrtf(s2 / (float)n + eps), b = coef[1] / sqrtf(s4 / (float)n + eps), c = coef[2] / sqrtf(s6 / (float)n + eps),
+                e = coef[3];
+    for (int i = threadIdx.x; i < n8; i += 256) {
+        const uint4 d = zr[i];
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&d);
+        uint4 o;
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float u = __low2float(p[k]), v = __high2float(p[k]);
+            q[k] = __floats2bfloat162_rn(fmaf(u, fmaf(u, fmaf(u, c, b), a), e), fmaf(v, fmaf(v, fmaf(v, c, b), a), e));
+        }
+        orow[i] = o;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ rotation of a slice of every head
 // dst[t, h, dst_off + i] = rotated src[t, h, src_off + i], i < width: the first rotary_dim values turn by the token's position (pairs by
 // `pairing`), the rest pass.  One thread per (token, head, pair or passing value).
@@ -210,6 +344,27 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ x, const float* __restrict__
     }
 }
 
+// bfloat16, cols % 4 == 0, gate rows 16-byte aligned: four values per thread
+__global__ void __launch_bounds__(256) sigmoid_gate_vec_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ gate, long long gate_ld, int cols,
+                                                               long long n_vec) {
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int per = cols >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / per;
+        const int c = (int)(i - t * per) << 2;
+        const float4 g = *reinterpret_cast<const float4*>(gate + t * gate_ld + c);
+        uint2* px = reinterpret_cast<uint2*>(x + t * cols + c);
+        const uint2 d = *px;
+        const __nv_bfloat162 d01 = *reinterpret_cast<const __nv_bfloat162*>(&d.x), d23 = *reinterpret_cast<const __nv_bfloat162*>(&d.y);
+        const __nv_bfloat162 o01 = __floats2bfloat162_rn(__low2float(d01) / (1.0f + expf(-g.x)), __high2float(d01) / (1.0f + expf(-g.y)));
+        const __nv_bfloat162 o23 = __floats2bfloat162_rn(__low2float(d23) / (1.0f + expf(-g.z)), __high2float(d23) / (1.0f + expf(-g.w)));
+        uint2 o;
+        o.x = *reinterpret_cast<const unsigned*>(&o01); o.y = *reinterpret_cast<const unsigned*>(&o23);
+        *px = o;
+    }
+}
+
 }  // namespace
 
 // h float32 [T, hid]; taps float32 [hid, K]; out [T, hid] in the activation dtype.  The kept inputs of every sequence of the step are moved on
@@ -232,7 +387,20 @@ VM_API int vm_input_conv(const float* h, const float* taps, float* state, long l
                           (__nv_bfloat16*)out, hid, K);
         return vm_launch_status();
     }
-    if (act_dtype == VM_F32)
+    const bool aligned = hid % 4 == 0 && state_stride % 4 == 0 && state_offset % 4 == 0 && ((uintptr_t)h | (uintptr_t)taps | (uintptr_t)state) % 16 == 0 &&
+                         (uintptr_t)out % 8 == 0;
+    if (act_dtype == VM_BF16 && aligned) {
+        const long long n_vec = (long long)T * (hid >> 2);
+        const dim3 grid((unsigned)((n_vec + 255) / 256));
+#define VM_CONV_VEC(KT)                                                                                                                              \
+    vm_launch_pdl(input_conv_vec_kernel<KT>, grid, dim3(256), 0, stream, h, taps, (const float*)state, state_stride, state_offset, seq_of_token, cu_tokens, \
+                  slots, (__nv_bfloat16*)out, hid, K, n_vec)
+        if (K == 2) VM_CONV_VEC(2);
+        else if (K == 3) VM_CONV_VEC(3);
+        else if (K == 4) VM_CONV_VEC(4);
+        else VM_CONV_VEC(0);
+#undef VM_CONV_VEC
+    } else if (act_dtype == VM_F32)
         vm_launch_pdl(input_conv_kernel<float>, dim3(T), dim3(threads), 0, stream, h, taps, (const float*)state, state_stride, state_offset, positions,
                       seq_of_token, cu_tokens, slots, (float*)out, hid, K);
     else
@@ -252,6 +420,11 @@ VM_API int vm_norm_residual_add(float* h, const void* y, long long ld, int y_dty
     const int threads = hid >= 512 ? 256 : 128;
     const size_t smem = (size_t)hid * sizeof(float);
     if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    if (y_dtype == VM_BF16 && T > 32 && hid % 4 == 0 && ld % 4 == 0 && ((uintptr_t)h | (uintptr_t)w) % 16 == 0 && (uintptr_t)y % 8 == 0) {
+        vm_launch_pdl(norm_residual_vec_kernel, dim3((T + NR_WARPS - 1) / NR_WARPS), dim3(NR_WARPS * 32), 0, stream, h, (const __nv_bfloat16*)y, ld, w, T, hid,
+                      eps);
+        return vm_launch_status();
+    }
     if (y_dtype == VM_F32) vm_launch_pdl(norm_residual_kernel<float>, dim3(T), dim3(threads), smem, stream, h, (const float*)y, ld, w, hid, eps);
     else if (y_dtype == VM_BF16)
         vm_launch_pdl(norm_residual_kernel<__nv_bfloat16>, dim3(T), dim3(threads), smem, stream, h, (const __nv_bfloat16*)y, ld, w, hid, eps);
@@ -292,6 +465,8 @@ VM_API int vm_polynorm(const void* z, int z_dtype, const float* coef, void* out,
         vm_launch_pdl(polynorm_kernel<float, float>, dim3(T), dim3(threads), 0, stream, (const float*)z, coef, (float*)out, n, eps);
     else if (z_dtype == VM_F32 && act_dtype == VM_BF16)
         vm_launch_pdl(polynorm_kernel<float, __nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const float*)z, coef, (__nv_bfloat16*)out, n, eps);
+    else if (z_dtype == VM_BF16 && act_dtype == VM_BF16 && n % 8 == 0 && ((uintptr_t)z | (uintptr_t)out) % 16 == 0)
+        vm_launch_pdl(polynorm_vec_kernel, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)z, coef, (__nv_bfloat16*)out, n, eps);
     else if (z_dtype == VM_BF16 && act_dtype == VM_BF16)
         vm_launch_pdl(polynorm_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (const __nv_bfloat16*)z, coef, (__nv_bfloat16*)out, n,
                       eps);
@@ -324,6 +499,12 @@ VM_API int vm_sigmoid_gate(void* x, const float* gate, long long gate_ld, int T,
     const long long n = (long long)T * cols;
     const long long want = (n + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (act_dtype == VM_BF16 && cols % 4 == 0 && gate_ld % 4 == 0 && (uintptr_t)gate % 16 == 0 && (uintptr_t)x % 8 == 0) {
+        const long long n_vec = n >> 2, want_vec = (n_vec + 255) / 256;
+        vm_launch_pdl(sigmoid_gate_vec_kernel, dim3((unsigned)(want_vec < 148 * 16 ? want_vec : 148 * 16)), dim3(256), 0, stream, (__nv_bfloat16*)x, gate,
+                      gate_ld, cols, n_vec);
+        return vm_launch_status();
+    }
     if (act_dtype == VM_F32) vm_launch_pdl(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, gate, gate_ld, cols, n);
     else if (act_dtype == VM_BF16)
         vm_launch_pdl(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, gate, gate_ld, cols, n);

@@ -100,6 +100,17 @@ inline void rotate_slice(const void* src, long long src_ld, int src_head, int sr
           "rotate_slice", ctx.stream);
 }
 
+// the heads' products of a step of few tokens in bfloat16, with the gate or the rotated tail that follows them (csrc/head_products.cu)
+inline void head_products_few(const void* x, long long x_ld, int x_head, const void* w, long long w_head, bool k_by_n, void* out, long long out_ld,
+                              int out_head, int N, int K, int H, const float* gate, long long gate_ld, int tail, const RotaryTable* rot,
+                              const StepContext& ctx) {
+    Timed t("head_products_few", ctx.stream);
+    const bool turns = tail > 0 && rot && rot->inv_freq;
+    check(vm_head_products_few(x, x_ld, x_head, w, w_head, k_by_n ? 1 : 0, out, out_ld, out_head, ctx.T, N, K, H, gate, gate_ld, tail, ctx.positions,
+                               turns ? rot->inv_freq : nullptr, turns ? rot->rotary_dim : 0, turns ? rot->pairing : 0, ctx.stream),
+          "head_products_few", ctx.stream);
+}
+
 inline void sigmoid_gate(void* x, const float* gate, long long gate_ld, int T, int cols, DType act, cudaStream_t s) {
     Timed t("sigmoid_gate", s);
     check(vm_sigmoid_gate(x, gate, gate_ld, T, cols, code(act), s), "sigmoid_gate", s);

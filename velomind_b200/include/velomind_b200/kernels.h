@@ -80,6 +80,13 @@ int vm_rotate_slice(const void* src, long long src_ld, int src_head, int src_off
                     cudaStream_t stream);
 int vm_sigmoid_gate(void* x, const float* gate, long long gate_ld, int T, int cols, int act_dtype, cudaStream_t stream);
 
+// ---- head_products.cu: per-head products of a step of few tokens (bfloat16): out[t, h, :N] = W_h x[t, h, :K], W_h = w + h * w_head stored
+// [K, N] (k_by_n) or [N, K]; with [N, K] an optional gate (out *= sigmoid(gate[t, h * N + n]), float32 rows), with [K, N] an optional tail
+// (out[t, h, N : N + tail] = x[t, h, K : K + tail], its first rotary_dim values turned by the token's position)
+int vm_head_products_few(const void* x, long long x_ld, int x_head, const void* w, long long w_head, int k_by_n, void* out, long long out_ld,
+                         int out_head, int T, int N, int K, int H, const float* gate, long long gate_ld, int tail, const int* positions,
+                         const float* inv_freq, int rotary_dim, int pairing, cudaStream_t stream);
+
 // ---- mlstm.cu: the matrix-memory recurrence with its output stage
 // proj float32 [T, ld]: q | k | v | g | x_i | x_f (H*D, H*D, H*V, H*V, H, H columns); state float32, per slot and head S [D, V], n [D], m;
 // out [T, H*V] in the activation dtype

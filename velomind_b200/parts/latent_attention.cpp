@@ -146,21 +146,29 @@ public:
         if (skinny_products) ops::skinny_linear(cq, nullptr, 0.f, up_q_.weight, ctx.T, q, static_cast<int>(q_cols), false, nullptr, ctx.err, ctx.stream);
         else up_q_.apply(ctx, cq, act, q, act, ctx.T, ctx.T_cap);
         ctx.give(cq);
-        void* o = attend(ctx, q, kv);
-        if (gate_) ops::sigmoid_gate(o, down + gate_col(), cols, ctx.T, H_ * V_, act, ctx.stream);
+        // few tokens: the heads' products in kernels of this library that take the rotation and the gate along
+        const bool own_products = act == DType::BF16 && ctx.T_cap <= 32 && D_ * 8 * 4 <= 48 * 1024 && Rkv_ * 8 * 4 <= 48 * 1024;
+        void* o = attend(ctx, q, kv, own_products, gate_ ? down + gate_col() : nullptr, cols);
+        if (gate_ && !own_products) ops::sigmoid_gate(o, down + gate_col(), cols, ctx.T, H_ * V_, act, ctx.stream);
         ctx.give(down);
         return o;
     }
 
-    // q [T, H*(D+R)] -> o [T, H*V] (a buffer the caller gives back); q is given back here
-    void* attend(StepContext& ctx, void* q, KVView kv) {
+    // q [T, H*(D+R)] -> o [T, H*V] (a buffer the caller gives back); q is given back here.  own_products: the per-head products run in
+    // this library's kernels for few tokens, which turn the query's rotated part and apply the gate (float32 rows of gate_ld) themselves.
+    void* attend(StepContext& ctx, void* q, KVView kv, bool own_products, const float* gate, long long gate_ld) {
         const DType act = ctx.act_dtype;
         // the key up-projection on the query's side: qa_h = [W_uk,h^T q_h | turned q_rot,h]
         const int Dk = Rkv_ + R_, Dq = D_ + R_;
         void* qa = ctx.take_tokens(static_cast<long long>(H_) * Dk, act);
-        ops::linear_batched(q, static_cast<long long>(H_) * Dq, Dq, up_k_.ptr, static_cast<long long>(D_) * Rkv_, /*w_is_k_by_n=*/true, qa,
-                            static_cast<long long>(H_) * Dk, Dk, act, ctx.T, Rkv_, D_, H_, ctx.stream);
-        if (R_ > 0) ops::rotate_slice(q, static_cast<long long>(H_) * Dq, Dq, D_, qa, static_cast<long long>(H_) * Dk, Dk, Rkv_, rotary_, R_, H_, ctx);
+        if (own_products) {
+            ops::head_products_few(q, static_cast<long long>(H_) * Dq, Dq, up_k_.ptr, static_cast<long long>(D_) * Rkv_, /*k_by_n=*/true, qa,
+                                   static_cast<long long>(H_) * Dk, Dk, Rkv_, D_, H_, nullptr, 0, R_, &rotary_, ctx);
+        } else {
+            ops::linear_batched(q, static_cast<long long>(H_) * Dq, Dq, up_k_.ptr, static_cast<long long>(D_) * Rkv_, /*w_is_k_by_n=*/true, qa,
+                                static_cast<long long>(H_) * Dk, Dk, act, ctx.T, Rkv_, D_, H_, ctx.stream);
+            if (R_ > 0) ops::rotate_slice(q, static_cast<long long>(H_) * Dq, Dq, D_, qa, static_cast<long long>(H_) * Dk, Dk, Rkv_, rotary_, R_, H_, ctx);
+        }
         ctx.give(q);
         void* att = ctx.take_tokens(static_cast<long long>(H_) * Rkv_, act);
         kv.v_pages = kv.k_pages;
@@ -176,8 +184,12 @@ public:
         ctx.give(qa);
         // the value up-projection on the output's side: o_h = W_uv,h (sum_j p_j c_j)
         void* o = ctx.take_tokens(static_cast<long long>(H_) * V_, act);
-        ops::linear_batched(att, static_cast<long long>(H_) * Rkv_, Rkv_, up_v_.ptr, static_cast<long long>(V_) * Rkv_, /*w_is_k_by_n=*/false, o,
-                            static_cast<long long>(H_) * V_, V_, act, ctx.T, V_, Rkv_, H_, ctx.stream);
+        if (own_products)
+            ops::head_products_few(att, static_cast<long long>(H_) * Rkv_, Rkv_, up_v_.ptr, static_cast<long long>(V_) * Rkv_, /*k_by_n=*/false, o,
+                                   static_cast<long long>(H_) * V_, V_, V_, Rkv_, H_, gate, gate_ld, 0, nullptr, ctx);
+        else
+            ops::linear_batched(att, static_cast<long long>(H_) * Rkv_, Rkv_, up_v_.ptr, static_cast<long long>(V_) * Rkv_, /*w_is_k_by_n=*/false, o,
+                                static_cast<long long>(H_) * V_, V_, act, ctx.T, V_, Rkv_, H_, ctx.stream);
         ctx.give(att);
         return o;
     }
