@@ -9,6 +9,8 @@
 //
 // The weights of a head are a few KB and every token of the step needs all of them: a block stages the rows of up to 8 tokens in
 // shared memory and reads its share of the head's weights once.
+#include <cstdint>
+
 #include "common.cuh"
 
 namespace {
@@ -20,6 +22,29 @@ __device__ __forceinline__ void stage_rows(const __nv_bfloat16* __restrict__ x, 
     for (int i = threadIdx.x; i < HP_TOKENS * K; i += blockDim.x) {
         const int r = i / K, k = i - r * K;
         xs[i] = t0 + r < T ? __bfloat162float(x[(size_t)(t0 + r) * x_ld + (size_t)h * x_head + k]) : 0.f;
+    }
+}
+
+// the values behind the K that were multiplied: turned in pairs (the first rotary_dim) or passed on
+__device__ __forceinline__ void turn_tail(const __nv_bfloat16* __restrict__ x, long long x_ld, int x_head, __nv_bfloat16* __restrict__ out, long long out_ld,
+                                          int out_head, int h, int t0, int T, int N, int K, int tail, const int* __restrict__ positions,
+                                          const float* __restrict__ inv_freq, int rotary_dim, int pairing) {
+    const int half = rotary_dim / 2, per = half + (tail - rotary_dim);
+    for (int i = threadIdx.x; i < HP_TOKENS * per; i += blockDim.x) {
+        const int r = i / per, j = i - r * per, t = t0 + r;
+        if (t >= T) continue;
+        const __nv_bfloat16* s = x + (size_t)t * x_ld + (size_t)h * x_head + K;
+        __nv_bfloat16* d = out + (size_t)t * out_ld + (size_t)h * out_head + N;
+        if (j >= half) {
+            d[rotary_dim + (j - half)] = s[rotary_dim + (j - half)];
+            continue;
+        }
+        const int ia = pairing == VM_PAIR_INTERLEAVED ? 2 * j : j, ib = pairing == VM_PAIR_INTERLEAVED ? 2 * j + 1 : j + half;
+        float sn, cs;
+        sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+        const float u = __bfloat162float(s[ia]), v = __bfloat162float(s[ib]);
+        d[ia] = __float2bfloat16_rn(u * cs - v * sn);
+        d[ib] = __float2bfloat16_rn(v * cs + u * sn);
     }
 }
 
@@ -52,25 +77,78 @@ head_product_kn_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int 
         for (int r = 0; r < HP_TOKENS; ++r)
             if (t0 + r < T) out[(size_t)(t0 + r) * out_ld + (size_t)h * out_head + n] = __float2bfloat16_rn(acc[r]);
     }
-    if (tail <= 0 || blockIdx.y != 0) return;
-    // the values behind the K that were multiplied: turned in pairs (the first rotary_dim) or passed on
-    const int half = rotary_dim / 2, per = half + (tail - rotary_dim);
-    for (int i = threadIdx.x; i < HP_TOKENS * per; i += blockDim.x) {
-        const int r = i / per, j = i - r * per, t = t0 + r;
-        if (t >= T) continue;
-        const __nv_bfloat16* s = x + (size_t)t * x_ld + (size_t)h * x_head + K;
-        __nv_bfloat16* d = out + (size_t)t * out_ld + (size_t)h * out_head + N;
-        if (j >= half) {
-            d[rotary_dim + (j - half)] = s[rotary_dim + (j - half)];
-            continue;
-        }
-        const int ia = pairing == VM_PAIR_INTERLEAVED ? 2 * j : j, ib = pairing == VM_PAIR_INTERLEAVED ? 2 * j + 1 : j + half;
-        float sn, cs;
-        sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
-        const float u = __bfloat162float(s[ia]), v = __bfloat162float(s[ib]);
-        d[ia] = __float2bfloat16_rn(u * cs - v * sn);
-        d[ib] = __float2bfloat16_rn(v * cs + u * sn);
+    if (tail > 0 && blockIdx.y == 0) turn_tail(x, x_ld, x_head, out, out_ld, out_head, h, t0, T, N, K, tail, positions, inv_freq, rotary_dim, pairing);
+}
+
+// The same product with paired columns and the sum split over the block's warps: warp g takes rows g, g + 8, ... of W_h, a lane two
+// neighbouring columns (one 4-byte load per row, four rows asked for ahead of their use), and the warps' parts are added in shared
+// memory.  Needs N even and 4-byte aligned head matrices.  grid (H, ceil(N / 64), ceil(T / 8)), 8 warps.
+constexpr int KN_COLS = 64, KN_GROUPS = 8, KN_AHEAD = 4;
+__global__ void __launch_bounds__(KN_GROUPS * 32)
+head_product_kn_pairs_kernel(const __nv_bfloat16* __restrict__ x, long long x_ld, int x_head, const __nv_bfloat16* __restrict__ w, long long w_head,
+                             __nv_bfloat16* __restrict__ out, long long out_ld, int out_head, int T, int N, int K, int tail,
+                             const int* __restrict__ positions, const float* __restrict__ inv_freq, int rotary_dim, int pairing) {
+    extern __shared__ __align__(16) float xs[];          // [HP_TOKENS][K], then the warps' parts [KN_GROUPS][HP_TOKENS][KN_COLS]
+    float* part = xs + HP_TOKENS * K;
+    const int h = blockIdx.x, g = threadIdx.x >> 5, lane = threadIdx.x & 31, n0 = blockIdx.y * KN_COLS, n = n0 + 2 * lane, t0 = blockIdx.z * HP_TOKENS;
+    const __nv_bfloat16* wh = w + (size_t)h * w_head;
+    const bool col = n < N;                              // (N is even: the pair's second column exists with its first)
+    // (weights are constants: the first rows may be asked for before the wait on the kernel that makes x)
+    __nv_bfloat162 ahead[KN_AHEAD];
+#pragma unroll
+    for (int u = 0; u < KN_AHEAD; ++u) {
+        const int k = g + KN_GROUPS * u;
+        ahead[u] = col && k < K ? *reinterpret_cast<const __nv_bfloat162*>(wh + (size_t)k * N + n) : __floats2bfloat162_rn(0.f, 0.f);
     }
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    stage_rows(x, x_ld, x_head, h, t0, T, K, xs);
+    __syncthreads();
+    float acc[HP_TOKENS][2];
+#pragma unroll
+    for (int r = 0; r < HP_TOKENS; ++r) acc[r][0] = acc[r][1] = 0.f;
+    for (int k0 = g; k0 < K; k0 += KN_GROUPS * KN_AHEAD) {
+        float a[KN_AHEAD], b[KN_AHEAD];
+#pragma unroll
+        for (int u = 0; u < KN_AHEAD; ++u) {
+            a[u] = __low2float(ahead[u]);
+            b[u] = __high2float(ahead[u]);
+            const int k = k0 + KN_GROUPS * (KN_AHEAD + u);
+            ahead[u] = col && k < K ? *reinterpret_cast<const __nv_bfloat162*>(wh + (size_t)k * N + n) : __floats2bfloat162_rn(0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < KN_AHEAD; ++u) {
+            const int k = k0 + KN_GROUPS * u;
+            if (k < K) {
+#pragma unroll
+                for (int r = 0; r < HP_TOKENS; ++r) {
+                    const float xv = xs[r * K + k];
+                    acc[r][0] = fmaf(xv, a[u], acc[r][0]);
+                    acc[r][1] = fmaf(xv, b[u], acc[r][1]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < HP_TOKENS; ++r)
+        *reinterpret_cast<float2*>(part + ((size_t)g * HP_TOKENS + r) * KN_COLS + 2 * lane) = make_float2(acc[r][0], acc[r][1]);
+    __syncthreads();
+    {   // warp r adds the parts of token t0 + r
+        const int r = g, t = t0 + r;
+        if (t < T && col) {
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int q = 0; q < KN_GROUPS; ++q) {
+                const float2 v = *reinterpret_cast<const float2*>(part + ((size_t)q * HP_TOKENS + r) * KN_COLS + 2 * lane);
+                s0 += v.x;
+                s1 += v.y;
+            }
+            __nv_bfloat16* o = out + (size_t)t * out_ld + (size_t)h * out_head + n;
+            o[0] = __float2bfloat16_rn(s0);
+            o[1] = __float2bfloat16_rn(s1);
+        }
+    }
+    if (tail > 0 && blockIdx.y == 0) turn_tail(x, x_ld, x_head, out, out_ld, out_head, h, t0, T, N, K, tail, positions, inv_freq, rotary_dim, pairing);
 }
 
 // W_h stored [N, K]: a warp owns output row n and its lanes share the sum.  grid (H, ceil(N / 8), ceil(T / 8)), 8 warps.
@@ -134,7 +212,12 @@ VM_API int vm_head_products_few(const void* x, long long x_ld, int x_head, const
     const size_t smem = (size_t)HP_TOKENS * K * sizeof(float);
     if (smem > 48 * 1024 || H > 65535) return VM_ERR_UNSUPPORTED;
     const unsigned tiles = (unsigned)((T + HP_TOKENS - 1) / HP_TOKENS);
-    if (k_by_n)
+    const size_t smem_pairs = smem + (size_t)KN_GROUPS * HP_TOKENS * KN_COLS * sizeof(float);
+    if (k_by_n && N % 2 == 0 && w_head % 2 == 0 && reinterpret_cast<uintptr_t>(w) % 4 == 0 && smem_pairs <= 48 * 1024)
+        vm_launch_pdl(head_product_kn_pairs_kernel, dim3(H, (N + KN_COLS - 1) / KN_COLS, tiles), dim3(KN_GROUPS * 32), smem_pairs, stream,
+                      (const __nv_bfloat16*)x, x_ld, x_head, (const __nv_bfloat16*)w, w_head, (__nv_bfloat16*)out, out_ld, out_head, T, N, K, tail, positions,
+                      inv_freq, rotary_dim, pairing);
+    else if (k_by_n)
         vm_launch_pdl(head_product_kn_kernel, dim3(H, (N + 127) / 128, tiles), dim3(128), smem, stream, (const __nv_bfloat16*)x, x_ld, x_head,
                       (const __nv_bfloat16*)w, w_head, (__nv_bfloat16*)out, out_ld, out_head, T, N, K, tail, positions, inv_freq, rotary_dim, pairing);
     else

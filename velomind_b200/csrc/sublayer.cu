@@ -144,7 +144,6 @@ __global__ void input_conv_step_kernel(const float* __restrict__ h, const float*
 // one block per token; y float32 or T, rows of ld elements
 template <typename Y>
 __global__ void norm_residual_kernel(float* __restrict__ h, const Y* __restrict__ y, long long ld, const float* __restrict__ w, int hid, float eps) {
-    extern __shared__ float row[];
     __shared__ float red[32];
     vm_pdl_launch_dependents();
     vm_pdl_wait();
@@ -153,12 +152,11 @@ __global__ void norm_residual_kernel(float* __restrict__ h, const Y* __restrict_
     float ss = 0.f;
     for (int i = threadIdx.x; i < hid; i += blockDim.x) {
         const float v = vm_to_float(yr[i]);
-        row[i] = v;
         ss += v * v;
     }
     ss = vm_block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
-    for (int i = threadIdx.x; i < hid; i += blockDim.x) h[(size_t)t * hid + i] += row[i] * inv * w[i];
+    for (int i = threadIdx.x; i < hid; i += blockDim.x) h[(size_t)t * hid + i] += vm_to_float(yr[i]) * inv * w[i];      // (the row comes out of L1 again)
 }
 
 // The same for bfloat16 y with hid % 4 == 0 and ld % 4 == 0: a warp per token, 8-byte loads of y (its second pass finds the row in L1),
@@ -195,39 +193,41 @@ norm_residual_vec_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict_
 }
 
 // The same sum for steps of one token per sequence, followed by the NEXT sublayer's input convolution on the row just made (a thread owns
-// its channels through both): h += rmsnorm(y) * w ; out = h + conv(h) with the kept inputs moved on.  grid (B).
+// its channel through both): h += rmsnorm(y) * w ; out = h + conv(h) with the kept inputs moved on.  grid (B, ceil(hid / blockDim)): every
+// block sums the squares of the token's whole row (a few KB out of L2) and then makes its own blockDim channels, so that a wide row is
+// spread over several SMs instead of walked by one block.
 template <typename Y, typename T>
 __global__ void norm_residual_conv_step_kernel(float* __restrict__ h, const Y* __restrict__ y, long long ld, const float* __restrict__ w, int hid, float eps,
                                                const float* __restrict__ taps, float* __restrict__ state, long long state_stride, int state_offset,
                                                const int* __restrict__ slots, T* __restrict__ out, int K) {
-    extern __shared__ float row[];
     __shared__ float red[32];
     vm_pdl_launch_dependents();
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    const bool mine = c < hid;
+    // weights are constants: they may be read before the wait on the kernel that makes y
+    const float* tw = taps + (size_t)(mine ? c : 0) * K;
+    const float wc = mine ? w[c] : 0.f, last = tw[K - 1];
     vm_pdl_wait();
-    const int t = blockIdx.x;
+    float* kept = state + (size_t)slots[t] * state_stride + state_offset;
     const Y* yr = y + (size_t)t * ld;
     float ss = 0.f;
     for (int i = threadIdx.x; i < hid; i += blockDim.x) {
         const float v = vm_to_float(yr[i]);
-        row[i] = v;
         ss += v * v;
     }
     ss = vm_block_sum(ss, red);
+    if (!mine) return;
     const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
-    float* kept = state + (size_t)slots[t] * state_stride + state_offset;
-    for (int c = threadIdx.x; c < hid; c += blockDim.x) {
-        const float x = h[(size_t)t * hid + c] + row[c] * inv * w[c];
-        h[(size_t)t * hid + c] = x;
-        const float* tw = taps + (size_t)c * K;
-        float acc = x * (1.0f + tw[K - 1]);
-        for (int j = 0; j < K - 1; ++j) {
-            const float v = kept[(size_t)j * hid + c];
-            acc = fmaf(tw[j], v, acc);
-            if (j > 0) kept[(size_t)(j - 1) * hid + c] = v;
-        }
-        if (K > 1) kept[(size_t)(K - 2) * hid + c] = x;
-        out[(size_t)t * hid + c] = vm_from_float<T>(acc);
+    const float x = h[(size_t)t * hid + c] + vm_to_float(yr[c]) * inv * wc;
+    h[(size_t)t * hid + c] = x;
+    float acc = x * (1.0f + last);
+    for (int j = 0; j < K - 1; ++j) {
+        const float v = kept[(size_t)j * hid + c];
+        acc = fmaf(tw[j], v, acc);
+        if (j > 0) kept[(size_t)(j - 1) * hid + c] = v;
     }
+    if (K > 1) kept[(size_t)(K - 2) * hid + c] = x;
+    out[(size_t)t * hid + c] = vm_from_float<T>(acc);
 }
 
 // ------------------------------------------------------------------------------------------------ polynomial activation with unit-rms powers
@@ -418,8 +418,7 @@ VM_API int vm_norm_residual_add(float* h, const void* y, long long ld, int y_dty
     if (T <= 0) return 0;
     if (hid <= 0 || ld < hid) return VM_ERR_BAD_ARG;
     const int threads = hid >= 512 ? 256 : 128;
-    const size_t smem = (size_t)hid * sizeof(float);
-    if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    const size_t smem = 0;
     if (y_dtype == VM_BF16 && T > 32 && hid % 4 == 0 && ld % 4 == 0 && ((uintptr_t)h | (uintptr_t)w) % 16 == 0 && (uintptr_t)y % 8 == 0) {
         vm_launch_pdl(norm_residual_vec_kernel, dim3((T + NR_WARPS - 1) / NR_WARPS), dim3(NR_WARPS * 32), 0, stream, h, (const __nv_bfloat16*)y, ld, w, T, hid,
                       eps);
@@ -441,16 +440,16 @@ VM_API int vm_norm_residual_conv_step(float* h, const void* y, long long ld, int
     if (hid <= 0 || ld < hid || K < 1 || K > 64 || (K > 1 && (!state || state_offset < 0 || state_offset + (long long)(K - 1) * hid > state_stride)))
         return VM_ERR_BAD_ARG;
     const int threads = hid >= 512 ? 256 : 128;
-    const size_t smem = (size_t)hid * sizeof(float);
-    if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
+    const size_t smem = 0;
+    const dim3 grid(B, (hid + threads - 1) / threads);
     if (y_dtype == VM_F32 && act_dtype == VM_F32)
-        vm_launch_pdl(norm_residual_conv_step_kernel<float, float>, dim3(B), dim3(threads), smem, stream, h, (const float*)y, ld, w, hid, eps, taps, state,
+        vm_launch_pdl(norm_residual_conv_step_kernel<float, float>, grid, dim3(threads), smem, stream, h, (const float*)y, ld, w, hid, eps, taps, state,
                       state_stride, state_offset, slots, (float*)out, K);
     else if (y_dtype == VM_F32 && act_dtype == VM_BF16)
-        vm_launch_pdl(norm_residual_conv_step_kernel<float, __nv_bfloat16>, dim3(B), dim3(threads), smem, stream, h, (const float*)y, ld, w, hid, eps, taps,
+        vm_launch_pdl(norm_residual_conv_step_kernel<float, __nv_bfloat16>, grid, dim3(threads), smem, stream, h, (const float*)y, ld, w, hid, eps, taps,
                       state, state_stride, state_offset, slots, (__nv_bfloat16*)out, K);
     else if (y_dtype == VM_BF16 && act_dtype == VM_BF16)
-        vm_launch_pdl(norm_residual_conv_step_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(B), dim3(threads), smem, stream, h, (const __nv_bfloat16*)y, ld, w,
+        vm_launch_pdl(norm_residual_conv_step_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(threads), smem, stream, h, (const __nv_bfloat16*)y, ld, w,
                       hid, eps, taps, state, state_stride, state_offset, slots, (__nv_bfloat16*)out, K);
     else return VM_ERR_UNSUPPORTED;
     return vm_launch_status();
