@@ -160,7 +160,7 @@ def wired_config(hidden, taps, mixer, ff, eps):
             "blocks": [block]}
 
 
-@pytest.mark.parametrize("taps", [1, 4, 7])
+@pytest.mark.parametrize("taps", [1, 2, 3, 4, 7])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_convolution_on_the_input_and_norm_on_the_output(taps, dtype, toy_plugin, tmp_path):
     """Strong taps, so that the kept inputs matter; pieces shorter than the taps' reach, single tokens, batches; the embedding's scale."""

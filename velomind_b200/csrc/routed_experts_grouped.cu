@@ -162,6 +162,32 @@ experts_down_grouped_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bf
 __global__ void silu_weighted_rows_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ act, int rows, int ff,
                                           const int* __restrict__ token_of_row, const int* __restrict__ row_of_pair, const float* __restrict__ weight,
                                           int top) {
+    if ((ff & 7) == 0) {                   // eight values a thread, 16-byte loads and stores; the row's weight is looked up once
+        const unsigned per = (unsigned)ff >> 3;
+        const size_t n8 = (size_t)rows * per;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+            const int row = (int)(i / per), c = (int)(i - (size_t)row * per) << 3;
+            const int tok = token_of_row[row];
+            unsigned o[4] = {0u, 0u, 0u, 0u};
+            if (tok >= 0) {
+                float w = 0.f;
+                for (int k = 0; k < top; ++k)
+                    if (row_of_pair[(size_t)tok * top + k] == row) w = weight[(size_t)tok * top + k];
+                const __nv_bfloat16* src = gate_up + (size_t)row * 2 * ff + c;
+                const uint4 gv = *reinterpret_cast<const uint4*>(src), uv = *reinterpret_cast<const uint4*>(src + ff);
+                const unsigned gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 g2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[k]));
+                    const float2 u2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[k]));
+                    const float g0 = w * g2.x, g1 = w * g2.y;
+                    o[k] = vm_pack_bf16(g0 / (1.0f + expf(-g0)) * (w * u2.x), g1 / (1.0f + expf(-g1)) * (w * u2.y));
+                }
+            }
+            *reinterpret_cast<uint4*>(act + (size_t)row * ff + c) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        return;
+    }
     const size_t n = (size_t)rows * ff;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const int row = (int)(i / ff), c = (int)(i - (size_t)row * ff);
@@ -295,7 +321,7 @@ VM_API int vm_experts_grouped_glu(const void* x, const void* w_up, const void* w
         if (st) return st;
     }
     if (glu == VM_GLU_SILU_WEIGHTED_INPUT) {
-        const size_t n = (size_t)rows * ff, want = n / 256 + 1;
+        const size_t n = (size_t)rows * ff, want = ((ff & 7) == 0 ? n / 8 : n) / 256 + 1;
         silu_weighted_rows_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, rows, ff,
                                                                                                token_of_row, row_of_pair, weight, top);
         st = vm_launch_status();

@@ -99,6 +99,66 @@ input_conv_vec_kernel(const float* __restrict__ h, const float* __restrict__ tap
     *reinterpret_cast<uint2*>(out + (size_t)t * hid + c) = o;
 }
 
+// Many tokens, 2 to 4 taps: a thread makes four neighbouring channels of RUN consecutive tokens and carries the K - 1 earlier rows along in
+// registers, so every row of the step is loaded once per thread that needs it as a halo and once as the token itself (K - 1 + RUN loads
+// for RUN tokens).  Where the next token belongs to another sequence the carried rows are fetched anew (from the step or the kept rows).
+template <int KT, int RUN>
+__global__ void __launch_bounds__(256)
+input_conv_run_kernel(const float* __restrict__ h, const float* __restrict__ taps, const float* __restrict__ state, long long state_stride,
+                      int state_offset, const int* __restrict__ seq_of_token, const int* __restrict__ cu_tokens, const int* __restrict__ slots,
+                      __nv_bfloat16* __restrict__ out, int hid, int T, long long n_vec) {
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n_vec) return;
+    const int per = hid >> 2;
+    const int g = (int)(idx / per), c = (int)(idx - (long long)g * per) << 2;
+    float tw[4 * KT];
+    {
+        const float4* w4 = reinterpret_cast<const float4*>(taps + (size_t)c * KT);
+#pragma unroll
+        for (int q = 0; q < KT; ++q) {
+            const float4 v = w4[q];
+            tw[4 * q] = v.x; tw[4 * q + 1] = v.y; tw[4 * q + 2] = v.z; tw[4 * q + 3] = v.w;
+        }
+    }
+    float4 win[KT - 1];                      // win[j]: the input KT - 1 - j tokens back
+    int seq_before = -1;
+#pragma unroll
+    for (int i = 0; i < RUN; ++i) {
+        const int t = g * RUN + i;
+        if (t >= T) break;
+        const int seq = seq_of_token[t];
+        if (seq != seq_before) {
+            const int in_step = t - cu_tokens[seq];
+            const float* kept = state + (size_t)slots[seq] * state_stride + state_offset;
+#pragma unroll
+            for (int j = 0; j < KT - 1; ++j) {
+                const int back = KT - 1 - j;
+                const float* src = back <= in_step ? h + (size_t)(t - back) * hid + c : kept + (size_t)(KT - 1 - back + in_step) * hid + c;
+                win[j] = *reinterpret_cast<const float4*>(src);
+            }
+            seq_before = seq;
+        }
+        const float4 x = *reinterpret_cast<const float4*>(h + (size_t)t * hid + c);
+        float4 acc;
+        acc.x = x.x * (1.0f + tw[0 * KT + KT - 1]); acc.y = x.y * (1.0f + tw[1 * KT + KT - 1]);
+        acc.z = x.z * (1.0f + tw[2 * KT + KT - 1]); acc.w = x.w * (1.0f + tw[3 * KT + KT - 1]);
+#pragma unroll
+        for (int j = 0; j < KT - 1; ++j) {
+            acc.x = fmaf(tw[0 * KT + j], win[j].x, acc.x); acc.y = fmaf(tw[1 * KT + j], win[j].y, acc.y);
+            acc.z = fmaf(tw[2 * KT + j], win[j].z, acc.z); acc.w = fmaf(tw[3 * KT + j], win[j].w, acc.w);
+        }
+        const __nv_bfloat162 o01 = __floats2bfloat162_rn(acc.x, acc.y), o23 = __floats2bfloat162_rn(acc.z, acc.w);
+        uint2 o;
+        o.x = *reinterpret_cast<const unsigned*>(&o01); o.y = *reinterpret_cast<const unsigned*>(&o23);
+        *reinterpret_cast<uint2*>(out + (size_t)t * hid + c) = o;
+#pragma unroll
+        for (int j = 0; j + 1 < KT - 1; ++j) win[j] = win[j + 1];
+        win[KT - 2] = x;
+    }
+}
+
 // grid (B, ceil(hid / threads)); a thread owns one channel of one sequence and moves its K - 1 kept inputs on by the step's tokens.
 // Row i of the new state is the input n - (K - 1) + i tokens into the step, or, before the step, row i + n of the old state; rows are
 // written in ascending order, so a row is read before it is overwritten.
@@ -389,7 +449,18 @@ VM_API int vm_input_conv(const float* h, const float* taps, float* state, long l
     }
     const bool aligned = hid % 4 == 0 && state_stride % 4 == 0 && state_offset % 4 == 0 && ((uintptr_t)h | (uintptr_t)taps | (uintptr_t)state) % 16 == 0 &&
                          (uintptr_t)out % 8 == 0;
-    if (act_dtype == VM_BF16 && aligned) {
+    if (act_dtype == VM_BF16 && aligned && K >= 2 && K <= 4 && T >= 64) {
+        constexpr int RUN = 4;
+        const long long n_vec = (long long)((T + RUN - 1) / RUN) * (hid >> 2);
+        const dim3 grid((unsigned)((n_vec + 255) / 256));
+#define VM_CONV_RUN(KT)                                                                                                                                   \
+    vm_launch_pdl(input_conv_run_kernel<KT, RUN>, grid, dim3(256), 0, stream, h, taps, (const float*)state, state_stride, state_offset, seq_of_token, cu_tokens, \
+                  slots, (__nv_bfloat16*)out, hid, T, n_vec)
+        if (K == 2) VM_CONV_RUN(2);
+        else if (K == 3) VM_CONV_RUN(3);
+        else VM_CONV_RUN(4);
+#undef VM_CONV_RUN
+    } else if (act_dtype == VM_BF16 && aligned) {
         const long long n_vec = (long long)T * (hid >> 2);
         const dim3 grid((unsigned)((n_vec + 255) / 256));
 #define VM_CONV_VEC(KT)                                                                                                                              \
