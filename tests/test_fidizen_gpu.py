@@ -190,6 +190,58 @@ def test_convolution_on_the_input_and_norm_on_the_output(taps, dtype, toy_plugin
     run_cuts(engine, requests, plain, cuts, 3e-5 if dtype == "float32" else 2.5e-2)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_of_unlike_wiring_hand_their_last_sum_on(dtype, toy_plugin, tmp_path):
+    """A layer with the norm on its outputs, one with the norm in front, a third of the first kind and a fourth without a feed-forward:
+    in a decode step each leaves its last sum (with or without a norm on it) to the layer behind it, and the last one to the model."""
+    import velomind_b200 as vm
+    eps = 1e-5
+    mixer = latent_args(64, 2, 16, 8, 16, 32, 32, 0.2, 40, eps=eps)
+    ff = {"hidden": 64, "intermediate": 96, "activation": "polynorm", "coefficients": "act", "eps": eps, "up": "up", "down": "down"}
+    cfg = wired_config(64, 3, mixer, ff, eps)
+    wired = cfg["blocks"][0]
+    front = {k: v for k, v in copy.deepcopy(wired).items() if k != "arrangement_args"}
+    front["arrangement"] = "prenorm"
+    alone = copy.deepcopy(wired)
+    alone["arrangement_args"]["feed_forward"] = 0
+    alone["feed_forward"] = {"kind": "none"}
+    alone["feed_forward_norm"] = {"kind": "none", "args": {}}
+    cfg["blocks"] = [wired, front, copy.deepcopy(wired), alone]
+    rng = np.random.default_rng(77)
+    w = random_tensors(vm.weight_table(cfg), rng, 0.25)
+    for name in w:
+        if "canon" in name:
+            w[name] = rng.normal(0.0, 0.7, w[name].shape).astype(np.float32)
+        if name.endswith("feed_forward.act"):
+            w[name] = np.array([0.5, 0.3, -0.2, 0.05], np.float32)
+    if dtype == "bfloat16":
+        w = rounded_to_bf16(w)
+    folder = write_model(str(tmp_path / "mixed"), cfg, w, as_bf16=dtype == "bfloat16")
+    engine = vm.Engine(vm.load_model(folder, dtype, "cuda:0"), 64 * 6, max_slots=3)
+    requests = S.make_requests(64, (70, 5, 90, 1), seed=14)
+    m = as_mixer_config(mixer)
+
+    def after(x, l, kind):
+        pre, norm1, norm2 = f"layers.{l}.", w[f"layers.{l}.mixer_norm.weight"], w.get(f"layers.{l}.feed_forward_norm.weight")
+        if kind == "front":
+            x = x + P.latent_attention(P.rms_norm(x, norm1, eps), w, pre + "mixer.", m, eps)
+            return x + P.dense(P.rms_norm(x, norm2, eps), w, pre + "feed_forward.", eps)
+        x = x + P.rms_norm(P.latent_attention(P.through_convolution(x, w[pre + "canon1"]), w, pre + "mixer.", m, eps), norm1, eps)
+        if kind == "alone":
+            return x
+        return x + P.rms_norm(P.dense(P.through_convolution(x, w[pre + "canon2"]), w, pre + "feed_forward.", eps), norm2, eps)
+
+    plain = {}
+    for rid, toks in requests.items():
+        x = w["embed.weight"].astype(np.float64)[toks] * 3.0
+        for l, kind in enumerate(("wired", "front", "wired", "alone")):
+            x = after(x, l, kind)
+        plain[rid] = x
+    cuts = standard_cuts(requests)
+    cuts["pieces"] = steps_in_pieces(requests, (2, 1, 1, 30, 1))
+    run_cuts(engine, requests, plain, cuts, 5e-5 if dtype == "float32" else 8e-2)      # (four layers of bfloat16 rounding)
+
+
 # ----------------------------------------------------------------------------- shaped: sharp scores, so that one key off shows
 def sharp_attention(tmp_path, vm, args, seed, name):
     """A latent-attention layer alone whose scores are spread wide: most queries give nearly all their weight to one or two keys, so a

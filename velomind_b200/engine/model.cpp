@@ -141,6 +141,12 @@ void DecoderModel::forward(StepContext& ctx) {
         pending = layers[plan.schedule[run].layer].block->forward(ctx, h, pending);
     }
     ctx.run = -1;
+    if (pending && ctx.pending_norm_weight) {        // the last layer's norm sits on its output: add its normed delta first
+        ops::norm_residual_add(h, pending, hid, ctx.act_dtype, ctx.pending_norm_weight, ctx.pending_norm_eps, ctx.T, static_cast<int>(hid), ctx.stream);
+        ctx.give(pending);
+        pending = nullptr;
+    }
+    ctx.pending_norm_weight = nullptr;
     // Final norm and head on the wanted rows (plus `pending`, a product not yet added to the residual stream).  A step that
     // wants no logits (a prompt cut into several steps) has a bucket of its own, so it asks for nothing here.
     if (ctx.R > 0) {

@@ -467,6 +467,10 @@ struct StepContext {
     bool one_token_each = false;
     bool capturing = false;                     // the step is being recorded: no choice may depend on lengths, only on shape
     int run = -1;                               // the schedule position that is running
+    // how the delta a layer left pending joins the stream: as it is (null), or as rmsnorm(delta) * weight with this eps
+    // (a layer whose norm sits on its sublayers' outputs leaves that norm to whoever adds the delta)
+    const float* pending_norm_weight = nullptr;
+    float pending_norm_eps = 0.f;
     float* logits = nullptr;                    // [R, vocab]
     DType act_dtype = DType::BF16;
     int* err = nullptr;                         // device error word

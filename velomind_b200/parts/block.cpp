@@ -4,6 +4,17 @@
 
 namespace vmb {
 
+// Add a delta that is still pending to the residual stream: as it is, or through the norm its layer left with it.
+static void settle_pending(StepContext& ctx, float* h, void* pending, long long hid) {
+    if (!pending) return;
+    if (ctx.pending_norm_weight)
+        ops::norm_residual_add(h, pending, hid, ctx.act_dtype, ctx.pending_norm_weight, ctx.pending_norm_eps, ctx.T, static_cast<int>(hid), ctx.stream);
+    else
+        ops::residual_add(h, pending, static_cast<long long>(ctx.T) * hid, ctx.act_dtype, ctx.stream);
+    ctx.pending_norm_weight = nullptr;
+    ctx.give(pending);
+}
+
 // h += mixer(norm(h)); h += feed_forward(norm(h))  (examples/common/llama/llama_graph.cpp:203-229).
 //
 // The residual stream h is float32.  Each sum is carried out by the norm kernel that follows it, so `forward` takes the
@@ -16,6 +27,10 @@ public:
 
     void* forward(StepContext& ctx, float* h, void* pending) override {
         const long long hid = hidden(ctx);
+        if (pending && ctx.pending_norm_weight) {   // a delta that joins the stream through its own layer's norm: added here, not by this layer's norm kernel
+            settle(ctx, h, pending, hid);
+            pending = nullptr;
+        }
         if (p_.mixer->can_fuse(ctx, *p_.mixer_norm)) {
             settle(ctx, h, pending, hid);
             p_.mixer->forward_fused(ctx, h, *p_.mixer_norm);
@@ -46,11 +61,7 @@ public:
 private:
     static long long hidden(const StepContext& ctx) { return ctx.hidden; }
     // add a delta that is still pending to the residual stream
-    static void settle(StepContext& ctx, float* h, void* pending, long long hid) {
-        if (!pending) return;
-        ops::residual_add(h, pending, static_cast<long long>(ctx.T) * hid, ctx.act_dtype, ctx.stream);
-        ctx.give(pending);
-    }
+    static void settle(StepContext& ctx, float* h, void* pending, long long hid) { settle_pending(ctx, h, pending, hid); }
     BlockParts p_;
     bool feed_forward_;
 };
@@ -90,27 +101,33 @@ public:
 
     void* forward(StepContext& ctx, float* h, void* pending) override {
         if (ctx.hidden != hidden_) throw ConfigError("arrangement 'output_norm': the stream's width is not the one it was built for");
-        if (pending) {                               // a layer of another wiring left its last sum to its successor
-            ops::residual_add(h, pending, static_cast<long long>(ctx.T) * hidden_, ctx.act_dtype, ctx.stream);
-            ctx.give(pending);
-        }
         const int base = p_.mixer->cache_need().state_floats;
         const Rms n1 = rms_of(*p_.mixer_norm);
         const long long n = static_cast<long long>(ctx.T) * hidden_;
         const bool copies = convolves() || ctx.act_dtype != DType::F32;      // (a float32 sublayer without a convolution reads the stream in place)
         void* x = ctx.take_tokens(hidden_, ctx.act_dtype);
-        read_stream(ctx, h, taps_mixer_, base, x, n);
+        if (pending && ctx.pending_norm_weight && joins_steps(ctx)) {
+            // a decode step after a layer of this wiring: its last sum and this mixer's convolution on the row just made, one launch
+            ops::norm_residual_conv_step(h, pending, ctx.act_dtype, ctx.pending_norm_weight, ctx.pending_norm_eps, static_cast<const float*>(taps_mixer_.ptr), K_,
+                                         base, ctx, x);
+            ctx.pending_norm_weight = nullptr;
+            ctx.give(pending);
+        } else {
+            settle_pending(ctx, h, pending, hidden_);    // (a layer of another wiring left its last sum to its successor)
+            read_stream(ctx, h, taps_mixer_, base, x, n);
+        }
         void* y = ctx.take_tokens(hidden_, ctx.act_dtype);
         p_.mixer->forward(ctx, copies ? x : h, y);
         ctx.give(x);
         if (!feed_forward_) {
+            if (joins_steps(ctx)) return leave(ctx, y, n1);
             ops::norm_residual_add(h, y, hidden_, ctx.act_dtype, n1.weight, n1.eps, ctx.T, hidden_, ctx.stream);
             ctx.give(y);
             return nullptr;
         }
         const Rms n2 = rms_of(*p_.feed_forward_norm);
         x = ctx.take_tokens(hidden_, ctx.act_dtype);
-        if (convolves() && ctx.one_token_each) {
+        if (joins_steps(ctx)) {
             // a decode step: the mixer's sum and the feed-forward's convolution on the row just made, one launch
             ops::norm_residual_conv_step(h, y, ctx.act_dtype, n1.weight, n1.eps, static_cast<const float*>(taps_ff_.ptr), K_, base + (K_ - 1) * hidden_, ctx, x);
         } else {
@@ -121,6 +138,7 @@ public:
         y = ctx.take_tokens(hidden_, ctx.act_dtype);
         p_.feed_forward->forward(ctx, copies ? x : h, y);
         ctx.give(x);
+        if (joins_steps(ctx)) return leave(ctx, y, n2);
         ops::norm_residual_add(h, y, hidden_, ctx.act_dtype, n2.weight, n2.eps, ctx.T, hidden_, ctx.stream);
         ctx.give(y);
         return nullptr;
@@ -131,6 +149,14 @@ private:
         const float* weight = nullptr;
         float eps = 0.f;
     };
+    // a decode step of a convolving layer: a sum and the next convolution go into one launch
+    bool joins_steps(const StepContext& ctx) const { return convolves() && ctx.one_token_each; }
+    // the layer's last delta stays pending with its norm: the next layer adds it (with its own convolution, if it is of this wiring)
+    static void* leave(StepContext& ctx, void* y, const Rms& norm) {
+        ctx.pending_norm_weight = norm.weight;
+        ctx.pending_norm_eps = norm.eps;
+        return y;
+    }
     static Rms rms_of(Norm& norm) {
         Rms r;
         if (!norm.as_rms(&r.weight, &r.eps)) throw ConfigError("arrangement 'output_norm': the norm on a sublayer's output must be a root-mean-square norm");
