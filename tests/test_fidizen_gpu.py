@@ -61,6 +61,9 @@ MECHANISMS = {
     # ... a latent of 128 with 16 rotated values, a window that spans three pages; a latent of 32 with 64
     "latent_tiles_wide": ("mixer", "latent_attention", latent_args(64, 2, 16, 16, 24, 32, 128, 0.2, 130)),
     "latent_tiles_rot": ("mixer", "latent_attention", latent_args(64, 3, 8, 64, 16, 32, 32, 0.1, 9)),
+    # a latent wider than any head the other attention kernels take (320 values behind every key, 520 in the next)
+    "latent_wide": ("mixer", "latent_attention", latent_args(64, 2, 16, 8, 24, 32, 320, 0.2, 45)),
+    "latent_wider": ("mixer", "latent_attention", latent_args(48, 3, 8, 16, 8, 16, 520, 0.3, 70)),
     # no window: every earlier token
     "latent_open": ("mixer", "latent_attention", latent_args(64, 4, 16, 4, 32, 24, 40, 0.25, 0)),
     # no rotated part: the latent is key and value at once, under a window and with a sink

@@ -161,7 +161,8 @@ int launch_biased(const void* q, int q_row_stride, const void* kpages, const voi
     const long long warps = (long long)n_tokens * H;
     const int blocks = (int)((warps + ATT_WARPS - 1) / ATT_WARPS);
     const size_t smem = (size_t)ATT_WARPS * Dk * sizeof(float);
-    const int epl = (Dv + 31) / 32;
+    int epl = (Dv + 31) / 32;                    // value columns a lane: 1 to 8, then 12, 16, 24 or 32 (values of up to 1,024)
+    if (epl > 8) epl = epl <= 12 ? 12 : epl <= 16 ? 16 : epl <= 24 ? 24 : 32;
 #define VM_ATT_CASE(E)                                                                                                                   \
     case E:                                                                                                                              \
         attn_biased_kernel<T, E><<<blocks, ATT_WARPS * 32, smem, stream>>>((const T*)q, q_row_stride, (const T*)kpages, (const T*)vpages, \
@@ -171,6 +172,7 @@ int launch_biased(const void* q, int q_row_stride, const void* kpages, const voi
         break;
     switch (epl) {
         VM_ATT_CASE(1) VM_ATT_CASE(2) VM_ATT_CASE(3) VM_ATT_CASE(4) VM_ATT_CASE(5) VM_ATT_CASE(6) VM_ATT_CASE(7) VM_ATT_CASE(8)
+        VM_ATT_CASE(12) VM_ATT_CASE(16) VM_ATT_CASE(24) VM_ATT_CASE(32)
         default: return VM_ERR_UNSUPPORTED;
     }
 #undef VM_ATT_CASE
@@ -220,7 +222,7 @@ VM_API int vm_attention_sink_generic(const void* q, int q_row_stride, const void
     const int v_stride = v_row_stride > 0 ? v_row_stride : Dv;
     if (v_stride < Dv) return VM_ERR_BAD_ARG;
     if (n_tokens <= 0) return 0;
-    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || Dk <= 0 || Dk > 1024 || Dv <= 0 || Dv > 256 || window < 0 || keep_first < 0) return VM_ERR_UNSUPPORTED;
+    if (H <= 0 || Hkv <= 0 || H % Hkv != 0 || Dk <= 0 || Dk > 2048 || Dv <= 0 || Dv > 1024 || window < 0 || keep_first < 0) return VM_ERR_UNSUPPORTED;
     if ((rel != nullptr) != (bucket_of != nullptr) || (rel && far < 0)) return VM_ERR_BAD_ARG;
     if (act_dtype == VM_F32)
         return launch_biased<float>(q, q_row_stride, kpages, vpages, block_table, max_blocks, positions, seq_of_token, rel, bucket_of, far, out, n_tokens, H,
