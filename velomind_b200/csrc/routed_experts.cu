@@ -195,7 +195,7 @@ __global__ void router_kernel(const void* __restrict__ x, const float* __restric
 template <typename T>
 __global__ void router_scored_kernel(const void* __restrict__ x, const float* __restrict__ norm_w, float eps, const float* __restrict__ w_router,
                                      const float* __restrict__ correction, int hidden, int n_out, int top, int group_count, int group_keep,
-                                     float scale, int score_kind, int* __restrict__ chosen, float* __restrict__ weight) {
+                                     int group_top, float scale, int score_kind, int* __restrict__ chosen, float* __restrict__ weight) {
     __shared__ float red[32];
     extern __shared__ __align__(16) float sm[];          // [hidden] input, [n_out] scores, [n_out] choice scores, [group_count] group scores
     float* xs = sm;
@@ -237,10 +237,25 @@ __global__ void router_scored_kernel(const void* __restrict__ x, const float* __
     __syncwarp();
     if (group_count > 1 && group_keep < group_count) {
         const int per = n_out / group_count;
+        // a group's score: the sum of its group_top largest scores (1: the largest).  Groups are scored on the scores themselves
+        // (with the correction, if any), also where the choice inside them goes by the logits.
+        const bool by_logit = score_kind == VM_SCORE_SIGMOID && !correction;
         for (int g = lane; g < group_count; g += 32) {
-            float best = -INFINITY;
-            for (int i = 0; i < per; ++i) best = fmaxf(best, ch[g * per + i]);
-            gs[g] = best;
+            float total = 0.f, last = INFINITY;
+            int last_at = -1;
+            for (int k = 0; k < group_top && k < per; ++k) {      // the k-th largest: the largest below (last, last_at) in the order (score descending, index ascending)
+                float best = -INFINITY;
+                int at = -1;
+                for (int i = 0; i < per; ++i) {
+                    const float v = by_logit ? sc[g * per + i] : ch[g * per + i];
+                    const bool after = v < last || (v == last && i > last_at);
+                    if (after && v > best) { best = v; at = i; }
+                }
+                total += best;
+                last = best;
+                last_at = at;
+            }
+            gs[g] = total;
         }
         __syncwarp();
         // a group stays if fewer than group_keep groups come before it in the order (score descending, index ascending)
@@ -316,7 +331,7 @@ __global__ void experts_up_kernel(const void* __restrict__ x, const float* __res
             kind[i] = act_kind;
         } else {
             wrow[i] = urow[i] = w_up_shared + (size_t)(r - top * ff) * hidden;
-            if (glu == VM_GLU_SILU_WEIGHTED_INPUT) urow[i] = wrow[i] + (size_t)ff_shared * hidden;      // the shared expert is gated too
+            if (glu >= VM_GLU_SILU_WEIGHTED_INPUT) urow[i] = wrow[i] + (size_t)ff_shared * hidden;      // the shared expert is gated too
             kind[i] = act_kind_shared;
         }
     }
@@ -329,7 +344,7 @@ __global__ void experts_up_kernel(const void* __restrict__ x, const float* __res
             if (r0 + i < rows) {
                 float v;
                 if (skip[i]) v = 0.f;
-                else if (glu == VM_GLU_SILU_WEIGHTED_INPUT) {
+                else if (glu >= VM_GLU_SILU_WEIGHTED_INPUT) {      // (VM_GLU_SILU: wgt stays 1, the weight is the down kernel's)
                     // W (w x) = w (W x): gate and up as the activation dtype holds them, the weight applied in float32
                     const float g = wgt[i] * vm_to_float(vm_from_float<T>(d[i])), uu = wgt[i] * vm_to_float(vm_from_float<T>(u[i]));
                     v = g / (1.0f + expf(-g)) * uu;
@@ -496,7 +511,16 @@ VM_API int vm_expert_router_scored(const void* x, const float* norm_w, float eps
 VM_API int vm_expert_router_scores(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
                                    int n_out, int top, int group_count, int group_keep, float scale, int score_kind, int* chosen, float* weight,
                                    int act_dtype, cudaStream_t stream) {
+    return vm_expert_router_groups(x, norm_w, eps, w_router, correction, T, hidden, n_out, top, group_count, group_keep, 1, scale, score_kind, chosen,
+                                   weight, act_dtype, stream);
+}
+
+// the same with the number of a group's largest scores whose sum is the group's score
+VM_API int vm_expert_router_groups(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
+                                   int n_out, int top, int group_count, int group_keep, int group_top, float scale, int score_kind, int* chosen,
+                                   float* weight, int act_dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (group_top < 1) return VM_ERR_BAD_ARG;
     if (score_kind != VM_SCORE_SOFTMAX && score_kind != VM_SCORE_SIGMOID) return VM_ERR_BAD_ARG;
     if (n_out <= 0 || top <= 0 || hidden <= 0 || group_count <= 0 || n_out % group_count || group_keep <= 0 || group_keep > group_count) return VM_ERR_BAD_ARG;
     if (top > (n_out / group_count) * group_keep) return VM_ERR_BAD_ARG;
@@ -504,10 +528,10 @@ VM_API int vm_expert_router_scores(const void* x, const float* norm_w, float eps
     if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
     if (act_dtype == VM_F32)
         vm_launch_pdl(router_scored_kernel<float>, dim3(T), dim3(256), smem, stream, x, norm_w, eps, w_router, correction, hidden, n_out, top, group_count,
-                      group_keep, scale, score_kind, chosen, weight);
+                      group_keep, group_top, scale, score_kind, chosen, weight);
     else if (act_dtype == VM_BF16)
         vm_launch_pdl(router_scored_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, x, norm_w, eps, w_router, correction, hidden, n_out, top,
-                      group_count, group_keep, scale, score_kind, chosen, weight);
+                      group_count, group_keep, group_top, scale, score_kind, chosen, weight);
     else return VM_ERR_UNSUPPORTED;
     return vm_launch_status();
 }

@@ -170,8 +170,8 @@ __global__ void silu_weighted_rows_kernel(const __nv_bfloat16* __restrict__ gate
             const int tok = token_of_row[row];
             unsigned o[4] = {0u, 0u, 0u, 0u};
             if (tok >= 0) {
-                float w = 0.f;
-                for (int k = 0; k < top; ++k)
+                float w = weight ? 0.f : 1.0f;          // (no weights: the unit itself)
+                for (int k = 0; weight && k < top; ++k)
                     if (row_of_pair[(size_t)tok * top + k] == row) w = weight[(size_t)tok * top + k];
                 const __nv_bfloat16* src = gate_up + (size_t)row * 2 * ff + c;
                 const uint4 gv = *reinterpret_cast<const uint4*>(src), uv = *reinterpret_cast<const uint4*>(src + ff);
@@ -194,8 +194,8 @@ __global__ void silu_weighted_rows_kernel(const __nv_bfloat16* __restrict__ gate
         const int tok = token_of_row[row];
         float v = 0.f;
         if (tok >= 0) {
-            float w = 0.f;
-            for (int k = 0; k < top; ++k)
+            float w = weight ? 0.f : 1.0f;
+            for (int k = 0; weight && k < top; ++k)
                 if (row_of_pair[(size_t)tok * top + k] == row) w = weight[(size_t)tok * top + k];
             const float g = w * __bfloat162float(gate_up[(size_t)row * 2 * ff + c]), u = w * __bfloat162float(gate_up[(size_t)row * 2 * ff + ff + c]);
             v = g / (1.0f + expf(-g)) * u;
@@ -320,10 +320,10 @@ VM_API int vm_experts_grouped_glu(const void* x, const void* w_up, const void* w
         st = vm_launch_status();
         if (st) return st;
     }
-    if (glu == VM_GLU_SILU_WEIGHTED_INPUT) {
+    if (glu >= VM_GLU_SILU_WEIGHTED_INPUT) {      // (VM_GLU_SILU: unit weights here, the routing weight in the combine)
         const size_t n = (size_t)rows * ff, want = ((ff & 7) == 0 ? n / 8 : n) / 256 + 1;
         silu_weighted_rows_kernel<<<(int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)act, rows, ff,
-                                                                                               token_of_row, row_of_pair, weight, top);
+                                                                                               token_of_row, row_of_pair, glu == VM_GLU_SILU ? nullptr : weight, top);
         st = vm_launch_status();
         if (st) return st;
     } else if (glu) {

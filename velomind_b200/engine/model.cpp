@@ -1,6 +1,7 @@
 // A decoder model built from a plan: embedding, layers run in the plan's order, final norm, head.
 // Nothing here names an architecture; the plan says which parts and which order.
 #include <cstdio>
+#include <cstdlib>
 
 #include "ops.h"
 
@@ -69,6 +70,9 @@ DecoderModel::DecoderModel(ModelPlan p) : plan(std::move(p)) {
     plan.validate();
     embedding = build_part_as<Embedding>("embedding", plan.embedding);
     for (const BlockSpec& b : plan.blocks) layers.emplace_back(b);
+    for (const Layer& l : layers)
+        if (plan.residual_streams > 1 && !l.block->mixes_streams())
+            throw ConfigError("a model with several copies of the residual stream needs a wiring that mixes them in every layer ('" + l.spec.arrangement + "' does not)");
     final_norm = build_part_as<Norm>("norm", plan.final_norm);
     head = build_part_as<Head>("head", plan.head);
 }
@@ -120,27 +124,82 @@ std::vector<CacheNeed> DecoderModel::cache_needs() const {
         need.state_floats += wiring;
         out.push_back(need);
     }
+    if (embedding->state_floats() > 0) {             // what the embedding keeps per sequence: one more state area behind the runs'
+        CacheNeed need;
+        need.state_floats = embedding->state_floats();
+        out.push_back(need);
+    }
     return out;
 }
 
 std::vector<int> DecoderModel::cache_shares() const {
     std::vector<int> out;
     for (const ScheduleEntry& e : plan.schedule) out.push_back(e.cache_of);
+    if (embedding->state_floats() > 0) out.push_back(-1);
     return out;
+}
+
+// Debugging aid: VELOMIND_B200_DUMP_STREAM=<file> appends, after every run of a layer, the residual stream of the step's tokens (the
+// sum of its copies) to that file as float32 [T, hidden].  It waits for the device after every layer, so it belongs with
+// VELOMIND_B200_SYNC=1 (no recorded steps); a delta that a layer left pending is not in the rows it writes.
+static const char* dump_stream_path() {
+    static const char* path = std::getenv("VELOMIND_B200_DUMP_STREAM");
+    return path && *path ? path : nullptr;
+}
+
+static void dump_stream(StepContext& ctx, const float* h, bool pending) {
+    if (ctx.capturing) return;
+    const size_t n = static_cast<size_t>(ctx.T) * ctx.hidden;
+    std::vector<float> sum(n, 0.f), one(n);
+    for (int s = 0; s < ctx.streams; ++s) {
+        ops::cuda_check(cudaMemcpyAsync(one.data(), h + s * ctx.stream_stride, n * sizeof(float), cudaMemcpyDeviceToHost, ctx.stream), "reading the residual stream");
+        ops::cuda_check(cudaStreamSynchronize(ctx.stream), "reading the residual stream");
+        for (size_t i = 0; i < n; ++i) sum[i] += one[i];
+    }
+    if (FILE* f = std::fopen(dump_stream_path(), "ab")) {
+        std::fwrite(sum.data(), sizeof(float), n, f);
+        std::fclose(f);
+    }
+    if (pending) std::fprintf(stderr, "velomind_b200: a layer left a delta pending; the dumped rows are without it\n");
 }
 
 // Run the step's tokens through every layer of the schedule; float32 logits [R, vocab] at ctx.logit_rows.
 void DecoderModel::forward(StepContext& ctx) {
     const long long hid = plan.hidden_size;
     ctx.hidden = plan.hidden_size;
-    float* h = static_cast<float*>(ctx.take_tokens(hid, DType::F32));
+    const int S = plan.residual_streams;
+    ctx.streams = S;
+    ctx.stream_stride = static_cast<long long>(ctx.T_cap) * hid;
+    ctx.state_offset = 0;
+    float* h = static_cast<float*>(ctx.take_tokens(hid * S, DType::F32));      // copy s of the stream: [T, hid] at h + s * stream_stride
+    ctx.run = static_cast<int>(plan.schedule.size());                          // the embedding's own state area, if it keeps one
     embedding->forward(ctx, ctx.tokens, h);
+    for (int s = 1; s < S; ++s)                                               // every copy starts as the embedding's output
+        ops::cuda_check(cudaMemcpyAsync(h + s * ctx.stream_stride, h, static_cast<size_t>(ctx.T) * hid * sizeof(float), cudaMemcpyDeviceToDevice, ctx.stream),
+                        "copying the residual stream");
     void* pending = nullptr;
     for (size_t run = 0; run < plan.schedule.size(); ++run) {
         ctx.run = static_cast<int>(run);
+        ctx.state_offset = 0;
         pending = layers[plan.schedule[run].layer].block->forward(ctx, h, pending);
+        if (dump_stream_path() && !ctx.capturing) {
+            if (pending && ctx.pending_mix) {        // (written into the copies now, so that the dumped rows hold it)
+                ops::streams_step(h, ctx, pending, ctx.pending_mix, ctx.pending_out, nullptr, nullptr, 0.f, nullptr);
+                ctx.give(pending);
+                pending = nullptr;
+                ctx.pending_mix = ctx.pending_out = nullptr;
+            }
+            dump_stream(ctx, h, pending != nullptr);
+        }
     }
     ctx.run = -1;
+    if (pending && ctx.pending_mix) {                // the last layer's result still has to be written into the copies of the stream
+        ops::streams_step(h, ctx, pending, ctx.pending_mix, ctx.pending_out, nullptr, nullptr, 0.f, nullptr);
+        ctx.give(pending);
+        pending = nullptr;
+    }
+    ctx.pending_mix = ctx.pending_out = nullptr;
+    if (S > 1 && ctx.R > 0) ops::streams_sum_rows(h, ctx.stream_stride, S, ctx.logit_rows, ctx.R, static_cast<int>(hid), ctx.stream);   // copy 0 <- the sum, at the wanted rows
     if (pending && ctx.pending_norm_weight) {        // the last layer's norm sits on its output: add its normed delta first
         ops::norm_residual_add(h, pending, hid, ctx.act_dtype, ctx.pending_norm_weight, ctx.pending_norm_eps, ctx.T, static_cast<int>(hid), ctx.stream);
         ctx.give(pending);

@@ -226,11 +226,11 @@ struct ExpertKind {
 };
 
 inline void expert_router_scored(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
-                                 int n_out, int top, int group_count, int group_keep, float scale, int score_kind, int* chosen, float* weight, DType act,
-                                 cudaStream_t s) {
+                                 int n_out, int top, int group_count, int group_keep, int group_top, float scale, int score_kind, int* chosen, float* weight,
+                                 DType act, cudaStream_t s) {
     Timed t("expert_router", s);
-    check(vm_expert_router_scores(x, norm_w, eps, w_router, correction, T, hidden, n_out, top, group_count, group_keep, scale, score_kind, chosen, weight,
-                                  code(act), s),
+    check(vm_expert_router_groups(x, norm_w, eps, w_router, correction, T, hidden, n_out, top, group_count, group_keep, group_top, scale, score_kind, chosen,
+                                  weight, code(act), s),
           "expert_router", s);
 }
 
@@ -429,6 +429,90 @@ inline void decode_advance(const int* sampled, int* tokens, int* positions, int*
                            cudaStream_t s) {
     Timed t("decode_advance", s);
     check(vm_decode_advance(sampled, tokens, positions, ctx_len, draw_step, history, iteration, B, s), "decode_advance", s);
+}
+
+// ---- several copies of the residual stream
+inline void streams_step(float* h, const StepContext& ctx, const void* y, const float* mix, const float* w_out, const float* w_in, const float* norm_w,
+                         float eps, void* out) {
+    Timed t("streams_step", ctx.stream);
+    check(vm_streams_step(h, ctx.stream_stride, ctx.streams, y, mix, w_out, w_in, norm_w, eps, out, ctx.T, ctx.hidden, code(ctx.act_dtype), ctx.stream),
+          "streams_step", ctx.stream);
+}
+inline void streams_sum_rows(float* h, long long stride, int S, const int* rows, int n_rows, int hid, cudaStream_t s) {
+    Timed t("streams_sum_rows", s);
+    check(vm_streams_sum_rows(h, stride, S, rows, n_rows, hid, s), "streams_sum_rows", s);
+}
+
+// where the running part keeps its own floats of a sequence: the run's state area, from ctx.state_offset on
+inline void need_state(const StepContext& ctx, long long floats, const char* who) {
+    if (!ctx.state() || ctx.state_floats() < ctx.state_offset + floats) throw CacheError(std::string(who) + ": the cache holds no state area of this part's size");
+}
+
+inline void embed_pairs(const DeviceTensor& table, const DeviceTensor& pairs, long long buckets, long long mul_prev, long long mul_cur, StepContext& ctx,
+                        float* out) {
+    Timed t("embed_pairs", ctx.stream);
+    need_state(ctx, 1, "embedding");
+    check(vm_embed_pairs(table.ptr, pairs.ptr, code(table.dtype), ctx.tokens, ctx.positions, ctx.seq_of_token, ctx.cu_tokens, ctx.slots,
+                         reinterpret_cast<int*>(ctx.state() + ctx.state_offset), ctx.state_floats(), out, ctx.T, ctx.B, ctx.hidden,
+                         static_cast<int>(table.rows()), buckets, mul_prev, mul_cur, ctx.one_token_each ? 1 : 0, ctx.err, ctx.stream),
+          "embed_pairs", ctx.stream);
+    if (!ctx.one_token_each) ++counters().own_launches;
+}
+
+// what mixer_prepare needs beside the step: the projections' layout and the options
+struct PrepareArgs {
+    const float* bias = nullptr;        // float32 [C] or null
+    const float* taps = nullptr;        // float32 [C, K] or null
+    int K = 0;
+    const float *q_norm = nullptr, *k_norm = nullptr;
+    float eps = 0.f;
+    RotaryTable rot;
+    int H = 0, G = 0, Dk = 0, Dv = 0;
+    bool values_are_keys = false;
+};
+inline void mixer_prepare(const float* proj, int ld, const PrepareArgs& a, StepContext& ctx, const KVView& kv, void* q_out) {
+    Timed t("mixer_prepare", ctx.stream);
+    const long long C = static_cast<long long>(a.H + a.G) * a.Dk + (a.values_are_keys ? 0 : static_cast<long long>(a.G) * a.Dv);
+    if (a.taps && a.K > 1) need_state(ctx, (a.K - 1) * C, "attention");
+    check(vm_mixer_prepare(proj, ld, a.bias, a.taps, a.K, ctx.state(), ctx.state_floats(), ctx.state_offset, a.q_norm, a.k_norm, a.eps, a.rot.inv_freq,
+                           a.rot.rotary_dim, a.rot.pairing, ctx.positions, ctx.seq_of_token, ctx.cu_tokens, ctx.slots, kv.block_table, kv.table_width, q_out,
+                           kv.owns ? kv.k_pages : nullptr, kv.owns ? kv.v_pages : nullptr, kv.owns ? kv.n_pages : 0, ctx.T, ctx.B, a.H, a.G, a.Dk, a.Dv,
+                           a.values_are_keys ? 1 : 0, ctx.one_token_each ? 1 : 0, code(ctx.act_dtype), ctx.err, ctx.stream),
+          "mixer_prepare", ctx.stream);
+    if (a.taps && a.K > 1 && !ctx.one_token_each) ++counters().own_launches;
+}
+inline void sigmoid_gate_heads(void* x, const float* g, int ldg, int T, int cols, int per, DType act, cudaStream_t s) {
+    Timed t("sigmoid_gate", s);
+    check(vm_sigmoid_gate_heads(x, g, ldg, T, cols, per, code(act), s), "sigmoid_gate", s);
+}
+inline void join_rows(const void* a, const void* b, const float* bias_a, float ca, float cb, const float* wa, const float* wb, float eps, void* out, int T,
+                      int cols, DType act, cudaStream_t s) {
+    Timed t("join_rows", s);
+    check(vm_join_rows(a, b, bias_a, ca, cb, wa, wb, eps, out, T, cols, code(act), s), "join_rows", s);
+}
+
+// linear attention with a decaying matrix memory over the running part's state
+struct MemoryArgs {
+    int q_off = 0, k_off = 0, v_off = 0;
+    const float* z = nullptr;           // decay logits float32 [T, ldz], or null: head_log_decay
+    int ldz = 0;
+    float tau = 1.f;
+    const float* head_log_decay = nullptr;
+    RotaryTable rot;
+    float q_scale = 1.f, k_scale = 1.f;
+    int H = 0, Dk = 0, Dv = 0;
+};
+inline void decayed_memory(const float* proj, int ld, const MemoryArgs& a, StepContext& ctx, float* o) {
+    Timed t("decayed_memory", ctx.stream);
+    need_state(ctx, static_cast<long long>(a.H) * a.Dk * a.Dv, "decayed_memory");
+    check(vm_decayed_memory(proj, ld, a.q_off, a.k_off, a.v_off, a.z, a.ldz, a.tau, a.head_log_decay, a.rot.inv_freq, a.rot.rotary_dim, a.rot.pairing,
+                            a.q_scale, a.k_scale, ctx.state(), ctx.state_floats(), ctx.state_offset, ctx.positions, ctx.cu_tokens, ctx.slots, o, ctx.T, ctx.B,
+                            a.H, a.Dk, a.Dv, ctx.stream),
+          "decayed_memory", ctx.stream);
+}
+inline void memory_output(const float* o, const float* g, int ldg, const float* w, float eps, void* out, int T, int H, int Dv, DType act, cudaStream_t s) {
+    Timed t("memory_output", s);
+    check(vm_memory_output(o, g, ldg, w, eps, out, T, H, Dv, code(act), s), "memory_output", s);
 }
 
 int sm_count();                     // streaming multiprocessors of the current device, asked once

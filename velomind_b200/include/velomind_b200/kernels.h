@@ -28,8 +28,9 @@ enum { VM_ACT_SILU = 0, VM_ACT_GELU_TANH = 1, VM_ACT_RELU_SQUARED = 2 };
 // mean square (vm_polynorm)
 enum { VM_ACT_POLYNORM = 16 };
 // gated experts: the clamped unit min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u) + 1); or silu(w g) (w u) with the routing weight w
-// on the expert's input (it is then not applied to the output again, and the shared expert is gated in the same way, with w = 1)
-enum { VM_GLU_NONE = 0, VM_GLU_CLAMPED = 1, VM_GLU_SILU_WEIGHTED_INPUT = 2 };
+// on the expert's input (it is then not applied to the output again, and the shared expert is gated in the same way, with w = 1); or the
+// plain SiLU-gated unit silu(g) u whose OUTPUT takes the routing weight (the shared expert gated too, with weight 1)
+enum { VM_GLU_NONE = 0, VM_GLU_CLAMPED = 1, VM_GLU_SILU_WEIGHTED_INPUT = 2, VM_GLU_SILU = 3 };
 // how a router that scores all its outputs scores them: softmax over all of them, or the sigmoid of each alone
 enum { VM_SCORE_SOFTMAX = 0, VM_SCORE_SIGMOID = 1 };
 // error words a kernel may leave in `err`
@@ -132,6 +133,10 @@ int vm_expert_router_scored(const void* x, const float* norm_w, float eps, const
 int vm_expert_router_scores(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
                             int n_out, int top, int group_count, int group_keep, float scale, int score_kind, int* chosen, float* weight, int act_dtype,
                             cudaStream_t stream);      // vm_expert_router_scored with the kind of score (VM_SCORE_*) as an argument
+// the same with the number of a group's largest scores that make up the group's score (1: its largest; 2: the sum of its two largest)
+int vm_expert_router_groups(const void* x, const float* norm_w, float eps, const float* w_router, const float* correction, int T, int hidden,
+                            int n_out, int top, int group_count, int group_keep, int group_top, float scale, int score_kind, int* chosen,
+                            float* weight, int act_dtype, cudaStream_t stream);
 
 // ---- attention_biased.cu: windowed attention with kept first tokens and a learned bias by bucketed distance; keys of Dk, values of Dv
 // qkv [T, ld]: H query heads and Hkv key heads of Dk, Hkv value heads of Dv; queries and keys get a unit-rms norm per head (weights wq, wk
@@ -255,6 +260,47 @@ int vm_tc_grouped_linear(const void* A, long long lda, const void* W, int M, int
 int vm_tc_qkv_rope(const void* A, long long lda, const void* W, int M, int K, void* q_out, const int* positions,
                    const int* seq_of_token, const int* block_table, int max_blocks, const float* inv_freq, int rot_dim,
                    int pairing, void* kpages, void* vpages, int H, int Hkv, int D, int n_pages, int* err, cudaStream_t stream);
+
+// ---- hyper.cu: several copies of the residual stream; an embedding with a table read by pairs of tokens
+// Copy s of the stream is [T, hid] float32 at h + s * stride.  y (activation dtype, or null): every copy becomes
+// sum_s mix[s, to] x_s + w_out[to] * y (mix float32 [S, S] indexed [from, to]).  out (activation dtype, or null) then gets
+// rmsnorm(sum_s w_in[s] x_s) * norm_w.  At most 8 copies.
+int vm_streams_step(float* h, long long stride, int S, const void* y, const float* mix, const float* w_out, const float* w_in, const float* norm_w,
+                    float eps, void* out, int T, int hid, int act_dtype, cudaStream_t stream);
+int vm_streams_sum_rows(float* h, long long stride, int S, const int* rows, int n_rows, int hid, cudaStream_t stream);   // copy 0 <- the sum, at `rows`
+// out[t] = table[token] + pairs[(previous * mul_prev + token * mul_cur) mod buckets], row `buckets` for a sequence's first token;
+// `last`: an int32 word per slot (last_stride words apart) that keeps the token before the next step's first one
+int vm_embed_pairs(const void* table, const void* pairs, int table_dtype, const int* tokens, const int* positions, const int* seq_of_token,
+                   const int* cu_tokens, const int* slots, int* last, long long last_stride, float* out, int T, int B, int hid, int vocab,
+                   long long buckets, long long mul_prev, long long mul_cur, int one_token_each, int* err, cudaStream_t stream);
+
+// ---- mixer_prep.cu: from an attention mixer's projections to its attention kernel (bias, short convolution over time with kept rows,
+// norm over the whole projection, rotary positions, cache write), and gates, biases and joins behind it
+// proj float32 [T, ld]: columns [0, H Dk) queries, then G Dk keys, then (unless the values are the keys) G Dv values; bias float32 [C]
+// or null; taps float32 [C, K] or null (the K - 1 rows kept per sequence lie in state [slot, state_stride] at state_offset);
+// q_norm [H Dk], k_norm [G Dk] or both null; inv_freq [rotary_dim / 2] or null.  q_out [T, H Dk] and the pages in the activation dtype.
+int vm_mixer_prepare(const float* proj, int ld, const float* bias, const float* taps, int K, float* state, long long state_stride, int state_offset,
+                     const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rotary_dim, int pairing, const int* positions,
+                     const int* seq_of_token, const int* cu_tokens, const int* slots, const int* block_table, int max_blocks, void* q_out, void* kpages,
+                     void* vpages, int n_pages, int T, int B, int H, int G, int Dk, int Dv, int values_are_keys, int one_token_each, int act_dtype,
+                     int* err, cudaStream_t stream);
+// x[t, c] *= sigmoid(g[t, c / per]), g float32 rows of stride ldg: one gate for every `per` neighbouring values (a head)
+int vm_sigmoid_gate_heads(void* x, const float* g, int ldg, int T, int cols, int per, int act_dtype, cudaStream_t stream);
+// out = ca f(a + bias_a) + cb f(b); f the identity or (wa, wb given) the RMS norm over the row with that weight; b null: the first term alone
+int vm_join_rows(const void* a, const void* b, const float* bias_a, float ca, float cb, const float* wa, const float* wb, float eps, void* out, int T,
+                 int cols, int act_dtype, cudaStream_t stream);
+
+// ---- decayed_memory.cu: linear attention with a decaying matrix memory S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t
+// proj float32 [T, ld] with queries at q_off ([H, Dk]), keys at k_off, values at v_off ([H, Dv]); z float32 [T, ldz] decay logits
+// (a = sigmoid(z)^(1 / tau)) or null with head_log_decay float32 [H]; inv_freq or null; the [H, Dk, Dv] memory of a sequence lies in
+// state [slot, state_stride] at state_offset; o float32 [T, H Dv]
+int vm_decayed_memory(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* head_log_decay,
+                      const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
+                      int state_offset, const int* positions, const int* cu_tokens, const int* slots, float* o, int T, int B, int H, int Dk, int Dv,
+                      cudaStream_t stream);
+// out[t, h] = o[t, h] / rms(o[t, h]) * w * silu(g[t, h]); w float32 [Dv] or null; g float32 rows of stride ldg
+int vm_memory_output(const float* o, const float* g, int ldg, const float* w, float eps, void* out, int T, int H, int Dv, int act_dtype,
+                     cudaStream_t stream);
 
 // ---- sampling.cu
 int vm_sample(const float* logits, long long row_stride, int R, int V, const float* temperature, const float* top_p,

@@ -175,6 +175,7 @@ struct ScheduleEntry {
 
 struct ModelPlan {
     int hidden_size = 0, vocab_size = 0;
+    int residual_streams = 1;                 // copies of the residual stream that the layers' wiring keeps (hyper-connections); 1: the usual one
     PartSpec embedding;
     std::string embedding_prefix;
     std::vector<BlockSpec> blocks;
@@ -458,6 +459,13 @@ struct KVView {
 struct StepContext {
     int T = 0, B = 0, R = 0, T_cap = 0, B_cap = 0, R_cap = 0;
     int hidden = 0;                             // width of the residual stream
+    // A model with several copies of the residual stream keeps copy s at h + s * stream_stride (each [T, hidden] float32); the
+    // embedding fills all of them alike, the layers' wiring mixes them, and their sum goes to the final norm.
+    int streams = 1;
+    long long stream_stride = 0;
+    // where, inside the run's per-sequence state area, the part that is running keeps its own floats: a mixer made of several
+    // mixers sets it before it runs each of them (0 for a mixer that is run alone)
+    int state_offset = 0;
     const int *tokens = nullptr, *positions = nullptr, *seq_of_token = nullptr, *cu_tokens = nullptr, *slots = nullptr,
               *ctx_len = nullptr, *logit_rows = nullptr;
     const int *host_positions = nullptr, *host_cu_tokens = nullptr, *host_ctx_len = nullptr, *host_slots = nullptr;
@@ -471,6 +479,9 @@ struct StepContext {
     // (a layer whose norm sits on its sublayers' outputs leaves that norm to whoever adds the delta)
     const float* pending_norm_weight = nullptr;
     float pending_norm_eps = 0.f;
+    // ... or, in a model with several copies of the stream, through the mixing its layer left with it: copy t becomes
+    // sum_s pending_mix[s, t] x_s + pending_out[t] * delta (device float32 [streams, streams] and [streams])
+    const float *pending_mix = nullptr, *pending_out = nullptr;
     float* logits = nullptr;                    // [R, vocab]
     DType act_dtype = DType::BF16;
     int* err = nullptr;                         // device error word
@@ -554,11 +565,16 @@ public:
     // float32 values the wiring itself keeps per sequence (the last inputs of a convolution over time); they lie behind the mixer's
     // own state in the run's state area, at offset mixer->cache_need().state_floats
     virtual int state_floats() const { return 0; }
+    // whether the wiring knows of several copies of the residual stream (a model that keeps more than one needs it of every layer)
+    virtual bool mixes_streams() const { return false; }
 };
 
 class Embedding : public Part {
 public:
     virtual void forward(StepContext& ctx, const int* tokens, float* h) = 0;
+    // float32 words the embedding keeps per sequence (the token before the step's first one); while it runs, `ctx.state()` is that
+    // area, which lies behind the schedule's own: a state area numbered schedule.size()
+    virtual int state_floats() const { return 0; }
 };
 
 class Head : public Part {

@@ -174,6 +174,86 @@ private:
     DeviceTensor taps_mixer_, taps_ff_;
 };
 
+// Several copies x_1 .. x_S of the residual stream (hyper-connections): a sublayer reads the norm of a weighted sum of the copies,
+// and its result y goes back into every copy while the copies are mixed:
+//     u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] * y     (all copies at once from the old ones)
+// with the tensors `<first>.in` [S], `<first>.out` [S], `<first>.mix` [S, S] (indexed [from, to]) for the mixer and `<second>.*` for the
+// feed-forward.  Sums, mixing and norm are float32.  A sublayer's write and the next sublayer's read are one kernel: the layer leaves
+// its last y pending with its `mix` and `out`, and whoever comes next (a layer of this wiring, or the model before its final norm)
+// carries the write out.
+class HyperConnections : public Arrangement {
+public:
+    HyperConnections(const BlockParts& p, int hidden, int streams, std::string first, std::string second, bool feed_forward)
+        : p_(p), hidden_(hidden), S_(streams), first_(std::move(first)), second_(std::move(second)), feed_forward_(feed_forward) {
+        if (hidden <= 0 || streams < 1 || streams > 8) throw ConfigError(format("arrangement 'hyper_connections': streams (%d) must be within 1..8", streams));
+    }
+    bool graph_safe() const override { return true; }
+    bool mixes_streams() const override { return true; }
+
+    WeightTable weight_specs() const override {
+        WeightTable t;
+        for (const std::string& n : names()) {
+            t[n + ".in"].shape = t[n + ".out"].shape = {S_};
+            t[n + ".mix"].shape = {S_, S_};
+        }
+        return t;
+    }
+    void bind(const Weights& w, BindContext& bc) override {
+        int i = 0;
+        for (const std::string& n : names()) {
+            in_[i] = bc.upload(w.at(n + ".in"), DType::F32);
+            out_[i] = bc.upload(w.at(n + ".out"), DType::F32);
+            mix_[i] = bc.upload(w.at(n + ".mix"), DType::F32);
+            ++i;
+        }
+    }
+
+    void* forward(StepContext& ctx, float* h, void* pending) override {
+        if (ctx.hidden != hidden_ || ctx.streams != S_) throw ConfigError("arrangement 'hyper_connections': the model's stream is not the one this layer was built for");
+        if (pending && !ctx.pending_mix) throw Error("arrangement 'hyper_connections': a layer of another wiring left a delta this layer cannot add");
+        const Rms n1 = rms_of(*p_.mixer_norm);
+        void* x = ctx.take_tokens(hidden_, ctx.act_dtype);
+        ops::streams_step(h, ctx, pending, ctx.pending_mix, ctx.pending_out, fp(in_[0]), n1.weight, n1.eps, x);
+        ctx.pending_mix = ctx.pending_out = nullptr;
+        ctx.give(pending);
+        void* y = ctx.take_tokens(hidden_, ctx.act_dtype);
+        p_.mixer->forward(ctx, x, y);
+        ctx.give(x);
+        if (!feed_forward_) return leave(ctx, y, 0);
+        const Rms n2 = rms_of(*p_.feed_forward_norm);
+        x = ctx.take_tokens(hidden_, ctx.act_dtype);
+        ops::streams_step(h, ctx, y, fp(mix_[0]), fp(out_[0]), fp(in_[1]), n2.weight, n2.eps, x);
+        ctx.give(y);
+        y = ctx.take_tokens(hidden_, ctx.act_dtype);
+        p_.feed_forward->forward(ctx, x, y);
+        ctx.give(x);
+        return leave(ctx, y, 1);
+    }
+
+private:
+    struct Rms {
+        const float* weight = nullptr;
+        float eps = 0.f;
+    };
+    static Rms rms_of(Norm& norm) {
+        Rms r;
+        if (!norm.as_rms(&r.weight, &r.eps)) throw ConfigError("arrangement 'hyper_connections': the norm in front of a sublayer must be a root-mean-square norm");
+        return r;
+    }
+    static const float* fp(const DeviceTensor& t) { return static_cast<const float*>(t.ptr); }
+    std::vector<std::string> names() const { return feed_forward_ ? std::vector<std::string>{first_, second_} : std::vector<std::string>{first_}; }
+    void* leave(StepContext& ctx, void* y, int which) {
+        ctx.pending_mix = fp(mix_[which]);
+        ctx.pending_out = fp(out_[which]);
+        return y;
+    }
+    BlockParts p_;
+    int hidden_, S_;
+    std::string first_, second_;
+    bool feed_forward_;
+    DeviceTensor in_[2], out_[2], mix_[2];
+};
+
 // The feed-forward of a layer that has none: no weights, never run.
 class NoFeedForward : public FeedForward {
 public:
@@ -193,6 +273,13 @@ struct Reg {
             return std::make_shared<OutputNormBlock>(parts, static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int_or(a, "taps", 0, k)),
                                                      arg_string_or(a, "mixer_conv", "", k), arg_string_or(a, "feed_forward_conv", "", k),
                                                      arg_int_or(a, "feed_forward", 1, k) != 0);
+        });
+        // several copies of the residual stream, read through weighted sums and mixed at every write
+        register_arrangement("hyper_connections", [](const json::Value& a, const BlockParts& parts) {
+            const char* k = "hyper_connections";
+            return std::make_shared<HyperConnections>(parts, static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "streams", k)),
+                                                      arg_string_or(a, "mixer_tensors", "hc1", k), arg_string_or(a, "feed_forward_tensors", "hc2", k),
+                                                      arg_int_or(a, "feed_forward", 1, k) != 0);
         });
         register_part("feed_forward", "none", [](const json::Value&) { return std::make_shared<NoFeedForward>(); });
     }

@@ -44,4 +44,15 @@ struct Linear {
     }
 };
 
+// out float32 [rows, N] = x W^T for a step's T rows of x in the activation dtype: few rows in bfloat16 stream the weights once
+// (the weight-streaming kernel with a float32 store), everything else is the library's product.
+inline void project_f32(StepContext& ctx, const Linear& lin, const void* x, float* out) {
+    const DeviceTensor& W = lin.weight;
+    if (ctx.act_dtype == DType::BF16 && W.dtype == DType::BF16 && lin.out_features % 8 == 0 && ops::skinny_ok(ctx.T, lin.in_features, W) &&
+        ctx.T_cap <= ops::skinny_max_rows(2 * W.rows() * W.cols()))
+        ops::skinny_linear(x, nullptr, 0.f, W, ctx.T, out, static_cast<int>(lin.out_features), true, nullptr, ctx.err, ctx.stream);
+    else
+        lin.apply(ctx, x, ctx.act_dtype, out, DType::F32, ctx.T, ctx.T_cap);
+}
+
 }  // namespace vmb

@@ -16,7 +16,8 @@
 // A third form of routing (`routing` = "sigmoid"): s = sigmoid(z), every output scored alone; the `top` largest are chosen and their
 // scores are the weights, not renormalised; there is no correction tensor unless `correction` = 1.  A third form of expert (`glu` = 2):
 // W_down (silu(W_gate h) * (W_up h)) where the routing weight multiplies the expert's INPUT, h = w x, not its output; the shared expert
-// (tensors shared.gate, shared.up, shared.down) has the same form and runs with w = 1, without a gate of its own.
+// (tensors shared.gate, shared.up, shared.down) has the same form and runs with w = 1, without a gate of its own.  `glu` = 3 is the same unit
+// with the routing weight on the expert's OUTPUT.  `groups_top` = n makes a group's score the sum of its n largest scores (default 1).
 #include "args.h"
 #include "linear.h"
 
@@ -32,7 +33,7 @@ int activation_code(const std::string& name, const char* part) {
 // how the router turns its outputs into chosen experts and weights
 struct Routing {
     bool scored = false;                 // false: softmax over the chosen logits; true: the form described above
-    int groups = 1, groups_keep = 1, identity = 0;
+    int groups = 1, groups_keep = 1, groups_top = 1, identity = 0;      // groups_top: a group's score is the sum of that many of its largest scores
     float scale = 1.f;
     int glu = VM_GLU_NONE;               // VM_GLU_*
     float limit = 0.f, alpha = 1.702f;
@@ -53,7 +54,8 @@ public:
         const int eligible = outputs / r.groups * r.groups_keep;
         if (top < 1 || top > eligible) throw ConfigError(format("part '%s': top (%d) must be within 1..%d, the outputs that can be chosen", k, top, eligible));
         if (r.glu == VM_GLU_CLAMPED && !(r.limit > 0)) throw ConfigError(format("part '%s': gated experts need a positive limit", k));
-        if (r.glu == VM_GLU_SILU_WEIGHTED_INPUT && (r.identity > 0 || gate_)) throw ConfigError(format("part '%s': experts with the weight on their input have neither identity experts nor a gated shared expert", k));
+        if (r.glu >= VM_GLU_SILU_WEIGHTED_INPUT && (r.identity > 0 || gate_)) throw ConfigError(format("part '%s': SiLU-gated experts have neither identity experts nor a gate on the shared expert", k));
+        if (r.groups_top < 1) throw ConfigError(format("part '%s': groups_top must be positive", k));
     }
 
     ops::ExpertKind kind() const {
@@ -67,7 +69,7 @@ public:
         return k;
     }
     bool general() const { return r_.scored || r_.glu; }      // the steps that take the general kernels
-    bool shared_glu() const { return r_.glu == VM_GLU_SILU_WEIGHTED_INPUT; }      // the shared expert has a gate matrix too
+    bool shared_glu() const { return r_.glu >= VM_GLU_SILU_WEIGHTED_INPUT; }      // the shared expert has a gate matrix too
 
     WeightTable weight_specs() const override {
         WeightTable t;
@@ -146,7 +148,7 @@ public:
         if (r_.scored) {
             if (gate_) throw Error("routed_experts: the scored router has no gate for a shared expert");
             ops::expert_router_scored(x, nw, eps, static_cast<const float*>(router_.ptr), r_.correction ? static_cast<const float*>(router_b_.ptr) : nullptr,
-                                      ctx.T, hidden_, E_ + r_.identity, top_, r_.groups, r_.groups_keep, r_.scale, r_.score_kind, chosen, weight,
+                                      ctx.T, hidden_, E_ + r_.identity, top_, r_.groups, r_.groups_keep, r_.groups_top, r_.scale, r_.score_kind, chosen, weight,
                                       ctx.act_dtype, ctx.stream);
             return;
         }
@@ -262,10 +264,11 @@ RegisterPart reg("feed_forward", "routed_experts", [](const json::Value& a) {
     r.correction = arg_int_or(a, "correction", routing == "scored" ? 1 : 0, k) != 0;
     r.groups = static_cast<int>(arg_int_or(a, "groups", 1, k));
     r.groups_keep = static_cast<int>(arg_int_or(a, "groups_keep", r.groups, k));
+    r.groups_top = static_cast<int>(arg_int_or(a, "groups_top", 1, k));
     r.identity = static_cast<int>(arg_int_or(a, "identity", 0, k));
     r.scale = static_cast<float>(arg_number_or(a, "scale", 1.0, k));
     r.glu = static_cast<int>(arg_int_or(a, "glu", 0, k));
-    if (r.glu < VM_GLU_NONE || r.glu > VM_GLU_SILU_WEIGHTED_INPUT) throw ConfigError("part 'routed_experts': glu is 0 (none), 1 (clamped) or 2 (SiLU, weight on the input)");
+    if (r.glu < VM_GLU_NONE || r.glu > VM_GLU_SILU) throw ConfigError("part 'routed_experts': glu is 0 (none), 1 (clamped), 2 (SiLU, weight on the input) or 3 (SiLU, weight on the output)");
     r.limit = static_cast<float>(arg_number_or(a, "limit", 0.0, k));
     r.alpha = static_cast<float>(arg_number_or(a, "alpha", 1.702, k));
     return std::make_shared<RoutedExperts>(static_cast<int>(arg_int(a, "hidden", k)), static_cast<int>(arg_int(a, "experts", k)),
