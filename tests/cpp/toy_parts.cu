@@ -374,6 +374,7 @@ ModelPlan probe_plan(const json::Value& data, const std::string& where) {
     plan.hidden_size = (int)r.integer("hidden");
     plan.vocab_size = (int)r.integer("vocab");
     plan.max_positions = (int)r.integer("limit");
+    if (r.has("streams")) plan.residual_streams = (int)r.integer("streams");      // copies of the residual stream
     auto part = [&](const json::Value& o, const char* key) {
         const json::Value* v = o.find(key);
         if (!v) throw ConfigError(where + ": missing part '" + key + "'");

@@ -64,6 +64,7 @@ json::Value part(const std::string& kind, const json::Value& args) {
 // {"kind": rotary_*, "args": {...}} from a mixer's "rot": {base, dims}
 json::Value rotation(const json::Value& mixer, long long dim, bool interleaved, const std::string& where) {
     KeyReader rot(need_object(mixer, "rot", where), where + ".rot");
+    if (rot.integer_or("dims", dim, 0) == 0) return part("none", json::Value());      // a rotation over no values
     json::Value a;
     a.set("head_dim", dim);
     a.set("theta", rot.number("base"));
