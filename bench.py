@@ -313,6 +313,36 @@ def fidizen_config(z, x):
             "layers": [{"type": "latent_attention", "mixer": att, "mlp": mlp} for mlp in (dense, moe, dense, moe)]}
 
 
+# ------------------------------------------------------------------------------------------------ --design vozetar
+# The same widths, four layers over three copies of the residual stream: attention (every earlier token, a convolution of three taps on
+# q, k and v, a sink, a gate per value) + gated unit; windowed attention with a sink beside retention + routed experts; windowed attention
+# whose values are its keys beside gated linear attention + gated unit; the second layer's kind once more + routed experts.  Beside it
+# Semesun (the closest design of this library: windowed attention with kept first tokens, a recurrent mixer with a matrix state, routed
+# experts in groups) and the Llama decoder at equal width and depth.
+VOZETAR_EXTRA = {
+    "w1024": dict(kv_heads=4, window=1024, keep_first=4, streams=3, mem_heads=8, mem_dim=64, mem_vdim=128, groups=2, keep=1, decay_rank=32),
+    "w2048": dict(kv_heads=8, window=1024, keep_first=4, streams=3, mem_heads=16, mem_dim=64, mem_vdim=128, groups=2, keep=1, decay_rank=32),
+}
+
+
+def vozetar_config(z, x):
+    rot = {"base": 10000.0, "dims": z["dim"]}
+    att = {"heads": z["heads"], "kv_heads": x["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5, "rot": rot}
+    mask = {"size": x["window"], "keep_first": x["keep_first"]}
+    ret = {"heads": x["mem_heads"], "dim": x["mem_dim"], "vdim": x["mem_vdim"], "rot": {"base": 10000.0, "dims": x["mem_dim"]},
+           "decay": [1.0 - 2.0 ** (-5 - 5.0 * i / max(1, x["mem_heads"] - 1)) for i in range(x["mem_heads"])]}
+    gla = {"heads": x["mem_heads"], "dim": x["mem_dim"], "vdim": x["mem_vdim"], "tau": 16.0, "decay_rank": x["decay_rank"]}
+    par = {"left": dict(att, mask=mask), "left_scale": 1.0, "right": ret, "right_scale": 1.0}
+    par2 = {"left": dict(att, mask=mask, conv=4), "right": gla}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": x["groups"], "keep": x["keep"]}}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    return {"architecture": "Vozetar", "vocab": z["vocab"], "width": z["width"], "streams": x["streams"], "norm": {"eps": 1e-6},
+            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 127, "mul_cur": 7}},
+            "layers": [{"type": "attention", "mixer": dict(att, conv=3), "mlp": dense}, {"type": "parallel", "mixer": par, "mlp": moe},
+                       {"type": "parallel_2", "mixer": par2, "mlp": dense}, {"type": "parallel", "mixer": par, "mlp": moe}]}
+
+
 def kogilix_attention_config(z):
     att = {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "q_rank": z["q_rank"], "kv_rank": z["kv_rank"], "scale": z["dim"] ** -0.5}
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared_ff"]}}
@@ -341,7 +371,7 @@ def op_table(vm, engine, entries):
 
 
 def design_arm(args):
-    """Prompt and decode throughput of a design (Kogilix, Semesun, Fidizen) at a few sizes, beside the library's other models at equal size."""
+    """Prompt and decode throughput of a design (Kogilix, Semesun, Fidizen, Vozetar) at a few sizes, beside the library's other models at equal size."""
     import numpy as np
     import velomind_b200 as vm
     T, B, prompt_len = 2048, 8, 512
@@ -354,6 +384,8 @@ def design_arm(args):
         models = [("kogilix", kogilix_config(z)), ("llama", llama_config_like(z))]
         if args.design == "semesun":
             models.insert(0, ("semesun", semesun_config(z, SEMESUN_EXTRA[name])))
+        if args.design == "vozetar":
+            models = [("vozetar", vozetar_config(z, VOZETAR_EXTRA[name])), ("semesun", semesun_config(z, SEMESUN_EXTRA[name])), ("llama", llama_config_like(z))]
         if args.design == "fidizen":
             models = [("fidizen", fidizen_config(z, FIDIZEN_EXTRA[name])), ("kogilix_attention", kogilix_attention_config(z)), ("llama", llama_config_like(z))]
         for which, cfg in models:
@@ -484,7 +516,7 @@ def main() -> int:
     ap.add_argument("--quick", action="store_true", help="skip the batch 1 / 64 points and the end-to-end run")
     ap.add_argument("--shape", default="135m", choices=sorted(SHAPES),
                     help="sizes of the random model: the benchmark's SmolLM2-135M (default), or the 360M / 1.7B shapes of the family")
-    ap.add_argument("--design", default="", choices=["", "kogilix", "semesun", "fidizen"],
+    ap.add_argument("--design", default="", choices=["", "kogilix", "semesun", "fidizen", "vozetar"],
                     help="instead of the benchmark: prompt and decode throughput of another design of the library at a few layer sizes, "
                          "beside the Llama decoder at equal size (one JSON line of its own)")
     args = ap.parse_args()

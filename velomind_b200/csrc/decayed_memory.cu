@@ -127,6 +127,308 @@ VM_API int vm_decayed_memory(const float* proj, int ld, int q_off, int k_off, in
     return vm_launch_status();
 }
 
+// ------------------------------------------------------------------------------------------------ prompts, chunk by chunk
+// Inside a chunk of C tokens the recurrence has a closed form.  With l_t = log a_t and b_t = l_(first) + .. + l_t (per key channel),
+//     o_t   = sum_(s <= t) [ sum_i q_t[i] k_s[i] exp(b_t[i] - b_s[i]) ] v_s  +  (q_t * exp(b_t))^T S_start
+//     S_end = diag(exp(b_last)) S_start + sum_s (k_s * exp(b_last - b_s)) v_s^T
+// and every exponent is <= 0.  Three passes: `local` computes for all chunks of all sequences and heads at once the first sum, the
+// chunk's own contribution to the memory, exp(b_last) and q * exp(b); `carry` walks each sequence's chunks elementwise and leaves the
+// memory at every chunk's start in place of the chunk's contribution; `finish`, parallel again, adds the second term.
+constexpr int DMC_THREADS = 256;
+
+// the chunk's sequence, its first token among the step's tokens and its number of tokens
+__device__ __forceinline__ bool dm_chunk_of(int chunk, const int* __restrict__ cu_tokens, int B, int C, int& seq, int& start, int& len) {
+    int before = 0;
+    for (int b = 0; b < B; ++b) {
+        const int n = cu_tokens[b + 1] - cu_tokens[b], nc = (n + C - 1) / C;
+        if (chunk < before + nc) {
+            const int c = chunk - before;
+            seq = b;
+            start = cu_tokens[b] + c * C;
+            len = min(C, n - c * C);
+            return true;
+        }
+        before += nc;
+    }
+    return false;
+}
+
+// grid (chunks, heads).  Shared: qT, kT, bT [Dk][C + 4] (channel-major, so that four neighbouring tokens are one 16-byte load),
+// v [C][Dv], A [C][C].  Dk and Dv are multiples of 4.
+template <int C>
+__global__ void __launch_bounds__(DMC_THREADS)
+dm_chunk_local_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ z, int ldz, float inv_tau,
+                      const float* __restrict__ head_log_decay, const float* __restrict__ inv_freq, int rotary_dim, int pairing, float q_scale,
+                      float k_scale, const int* __restrict__ positions, const int* __restrict__ cu_tokens, int B, float* __restrict__ o,
+                      float* __restrict__ dS, float* __restrict__ decay_all, float* __restrict__ q_decayed, int H, int Dk, int Dv) {
+    constexpr int CP = C + 4;
+    extern __shared__ __align__(16) float sm[];
+    float* qT = sm;
+    float* kT = qT + (size_t)Dk * CP;
+    float* bT = kT + (size_t)Dk * CP;
+    float* vs = bT + (size_t)Dk * CP;
+    float* A = vs + (size_t)C * Dv;
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    int seq, start, len;
+    if (!dm_chunk_of(blockIdx.x, cu_tokens, B, C, seq, start, len)) return;
+    const int h = blockIdx.y, tid = threadIdx.x;
+    const bool per_channel = z != nullptr;
+    // a. queries, keys (turned and scaled) and log decays, channel-major; values
+    for (int idx = tid; idx < C * Dk; idx += DMC_THREADS) {
+        const int t = idx / Dk, i = idx - t * Dk;
+        float q = 0.f, k = 0.f, l = 0.f;
+        if (t < len) {
+            const size_t tok = (size_t)start + t;
+            const float* row = proj + tok * ld;
+            const int pos = positions[tok];
+            q = dm_turned(row + q_off + (size_t)h * Dk, i, pos, inv_freq, rotary_dim, pairing) * q_scale;
+            k = dm_turned(row + k_off + (size_t)h * Dk, i, pos, inv_freq, rotary_dim, pairing) * k_scale;
+            l = dm_log_decay(head_log_decay, z, ldz, inv_tau, tok, h, Dk, i);
+        }
+        qT[i * CP + t] = q;
+        kT[i * CP + t] = k;
+        bT[i * CP + t] = l;
+    }
+    for (int idx = tid; idx < C * Dv; idx += DMC_THREADS) {
+        const int t = idx / Dv, j = idx - t * Dv;
+        vs[idx] = t < len ? proj[((size_t)start + t) * ld + v_off + (size_t)h * Dv + j] : 0.f;
+    }
+    __syncthreads();
+    // b. running sums of the log decays along the chunk
+    for (int i = tid; i < Dk; i += DMC_THREADS) {
+        float run = 0.f;
+        for (int t = 0; t < C; ++t) {
+            run += bT[i * CP + t];
+            bT[i * CP + t] = run;
+        }
+    }
+    __syncthreads();
+    // c. A[t][s] = sum_i q_t[i] k_s[i] exp(b_t[i] - b_s[i]) for s <= t, in tiles of 4 x 4 (tiles wholly above the diagonal are never read)
+    for (int tile = tid; tile < (C / 4) * (C / 4); tile += DMC_THREADS) {
+        const int t0 = (tile / (C / 4)) * 4, s0 = (tile % (C / 4)) * 4;
+        if (s0 > t0 + 3 || t0 >= len) continue;
+        float acc[4][4] = {};
+        if (per_channel) {
+            for (int i = 0; i < Dk; ++i) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qT + i * CP + t0), k4 = *reinterpret_cast<const float4*>(kT + i * CP + s0);
+                const float4 bt = *reinterpret_cast<const float4*>(bT + i * CP + t0), bs = *reinterpret_cast<const float4*>(bT + i * CP + s0);
+                const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w};
+                const float ba[4] = {bt.x, bt.y, bt.z, bt.w}, bb[4] = {bs.x, bs.y, bs.z, bs.w};
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qa[a] * ka[b], __expf(fminf(ba[a] - bb[b], 0.f)), acc[a][b]);
+            }
+        } else {
+            for (int i = 0; i < Dk; ++i) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qT + i * CP + t0), k4 = *reinterpret_cast<const float4*>(kT + i * CP + s0);
+                const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qa[a], ka[b], acc[a][b]);
+            }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] *= expf(fminf(bT[t0 + a] - bT[s0 + b], 0.f));      // (every channel has the same sums)
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) A[(t0 + a) * C + s0 + b] = (s0 + b <= t0 + a) ? acc[a][b] : 0.f;
+    }
+    __syncthreads();
+    // d. what the finish pass and the carry pass need: q * exp(b), exp(b_last); keys scaled to the chunk's end, in place
+    const size_t ch = (size_t)blockIdx.x * H + h;
+    for (int idx = tid; idx < Dk * C; idx += DMC_THREADS) {
+        const int i = idx / C, t = idx - i * C;
+        const float b = bT[i * CP + t];
+        q_decayed[ch * Dk * C + idx] = qT[i * CP + t] * expf(b);
+        kT[i * CP + t] = t < len ? kT[i * CP + t] * expf(bT[i * CP + len - 1] - b) : 0.f;
+    }
+    for (int i = tid; i < Dk; i += DMC_THREADS) decay_all[ch * Dk + i] = expf(bT[i * CP + len - 1]);
+    __syncthreads();
+    // e. o_t = sum_(s <= t) A[t][s] v_s, tiles of 4 tokens x 4 values
+    for (int tile = tid; tile < (C / 4) * (Dv / 4); tile += DMC_THREADS) {
+        const int t0 = (tile / (Dv / 4)) * 4, j0 = (tile % (Dv / 4)) * 4;
+        if (t0 >= len) continue;
+        float acc[4][4] = {};
+        const int s_end = min(t0 + 4, len);
+        for (int s = 0; s < s_end; ++s) {
+            const float4 v4 = *reinterpret_cast<const float4*>(vs + s * Dv + j0);
+            const float va[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float w = A[(t0 + a) * C + s];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(w, va[b], acc[a][b]);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+            if (t0 + a < len)
+                *reinterpret_cast<float4*>(o + ((size_t)start + t0 + a) * ((size_t)H * Dv) + (size_t)h * Dv + j0) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    }
+    // f. the chunk's contribution to the memory: sum_s (k_s exp(b_last - b_s)) v_s^T, tiles of 4 channels x 4 values
+    for (int tile = tid; tile < (Dk / 4) * (Dv / 4); tile += DMC_THREADS) {
+        const int i0 = (tile / (Dv / 4)) * 4, j0 = (tile % (Dv / 4)) * 4;
+        float acc[4][4] = {};
+        for (int s = 0; s < len; ++s) {
+            const float4 v4 = *reinterpret_cast<const float4*>(vs + s * Dv + j0);
+            const float va[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float w = kT[(i0 + a) * CP + s];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(w, va[b], acc[a][b]);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+            *reinterpret_cast<float4*>(dS + (ch * Dk + i0 + a) * Dv + j0) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+    }
+}
+
+// grid (sequences, heads, slices of the memory's values); a thread walks one value of the memory through its sequence's chunks
+template <int C>
+__global__ void dm_chunk_carry_kernel(float* __restrict__ dS, const float* __restrict__ decay_all, float* __restrict__ state, long long state_stride,
+                                      int state_offset, const int* __restrict__ cu_tokens, const int* __restrict__ slots, int H, int Dk, int Dv) {
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= Dk * Dv) return;
+    int first = 0;
+    for (int b = 0; b < seq; ++b) first += (cu_tokens[b + 1] - cu_tokens[b] + C - 1) / C;
+    const int nc = (cu_tokens[seq + 1] - cu_tokens[seq] + C - 1) / C;
+    if (nc <= 0) return;
+    float* S = state + (size_t)slots[seq] * state_stride + state_offset + (size_t)h * Dk * Dv + e;
+    float cur = *S;
+    const int i = e / Dv;
+    for (int c = 0; c < nc; ++c) {
+        const size_t ch = (size_t)(first + c) * H + h;
+        const float add = dS[ch * Dk * Dv + e];
+        dS[ch * Dk * Dv + e] = cur;                       // the memory at this chunk's start, for the finish pass
+        cur = fmaf(decay_all[ch * Dk + i], cur, add);
+    }
+    *S = cur;
+}
+
+// grid (chunks, heads, slices of VS values): o_t += (q_t exp(b_t))^T S_start
+template <int C>
+__global__ void __launch_bounds__(DMC_THREADS)
+dm_chunk_finish_kernel(const float* __restrict__ q_decayed, const float* __restrict__ S_start, const int* __restrict__ cu_tokens, int B,
+                       float* __restrict__ o, int H, int Dk, int Dv, int VS) {
+    extern __shared__ __align__(16) float sm[];
+    float* qT = sm;                          // [Dk][C]
+    float* S = sm + (size_t)Dk * C;          // [Dk][VS]
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    int seq, start, len;
+    if (!dm_chunk_of(blockIdx.x, cu_tokens, B, C, seq, start, len)) return;
+    const int h = blockIdx.y, j_base = blockIdx.z * VS, tid = threadIdx.x;
+    const int width = min(VS, Dv - j_base);
+    const size_t ch = (size_t)blockIdx.x * H + h;
+    for (int idx = tid; idx < Dk * C; idx += DMC_THREADS) qT[idx] = q_decayed[ch * Dk * C + idx];
+    for (int idx = tid; idx < Dk * width; idx += DMC_THREADS) {
+        const int i = idx / width, j = idx - i * width;
+        S[i * VS + j] = S_start[(ch * Dk + i) * Dv + j_base + j];
+    }
+    __syncthreads();
+    for (int tile = tid; tile < (C / 4) * (width / 4); tile += DMC_THREADS) {
+        const int t0 = (tile / (width / 4)) * 4, j0 = (tile % (width / 4)) * 4;
+        if (t0 >= len) continue;
+        float acc[4][4] = {};
+        for (int i = 0; i < Dk; ++i) {
+            const float4 q4 = *reinterpret_cast<const float4*>(qT + i * C + t0), s4 = *reinterpret_cast<const float4*>(S + i * VS + j0);
+            const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, sa[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qa[a], sa[b], acc[a][b]);
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+            if (t0 + a < len) {
+                float4* dst = reinterpret_cast<float4*>(o + ((size_t)start + t0 + a) * ((size_t)H * Dv) + (size_t)h * Dv + j_base + j0);
+                float4 v = *dst;
+                v.x += acc[a][0]; v.y += acc[a][1]; v.z += acc[a][2]; v.w += acc[a][3];
+                *dst = v;
+            }
+    }
+}
+
+// tokens per chunk for these sizes (0: the chunked form does not take them), and the scratch it needs
+static int dm_chunk_tokens(int Dk, int Dv) {
+    if (Dk % 4 || Dv % 4) return 0;
+    for (int C = 64; C >= 16; C /= 2) {
+        const size_t local = ((size_t)3 * Dk * (C + 4) + (size_t)C * Dv + (size_t)C * C) * sizeof(float);
+        const size_t finish = ((size_t)Dk * C + (size_t)Dk * (Dv < 128 ? Dv : 128)) * sizeof(float);
+        if (local <= 200 * 1024 && finish <= 200 * 1024) return C;
+    }
+    return 0;
+}
+
+VM_API int vm_decayed_memory_chunk_tokens(int Dk, int Dv) { return dm_chunk_tokens(Dk, Dv); }
+
+// float32 words of scratch for a step of up to T tokens in up to B sequences
+VM_API long long vm_decayed_memory_scratch_floats(int T, int B, int H, int Dk, int Dv) {
+    const int C = dm_chunk_tokens(Dk, Dv);
+    if (C == 0) return 0;
+    const long long chunks = T / C + B;
+    return chunks * H * ((long long)Dk * Dv + Dk + (long long)Dk * C);
+}
+
+template <int C>
+static int dm_launch_chunks(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float inv_tau, const float* head_log_decay,
+                            const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
+                            int state_offset, const int* positions, const int* cu_tokens, const int* slots, float* o, float* scratch, int n_chunks, int B,
+                            int H, int Dk, int Dv, cudaStream_t stream) {
+    float* dS = scratch;
+    float* decay_all = dS + (size_t)n_chunks * H * Dk * Dv;
+    float* q_decayed = decay_all + (size_t)n_chunks * H * Dk;
+    const size_t local = ((size_t)3 * Dk * (C + 4) + (size_t)C * Dv + (size_t)C * C) * sizeof(float);
+    const int VS = Dv < 128 ? Dv : 128;
+    const size_t finish = ((size_t)Dk * C + (size_t)Dk * VS) * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(dm_chunk_local_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)local);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(dm_chunk_finish_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)finish);
+    if (e != cudaSuccess) return (int)e;
+    vm_launch_pdl(dm_chunk_local_kernel<C>, dim3(n_chunks, H), dim3(DMC_THREADS), local, stream, proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, head_log_decay,
+                  inv_freq, rotary_dim, pairing, q_scale, k_scale, positions, cu_tokens, B, o, dS, decay_all, q_decayed, H, Dk, Dv);
+    int st = vm_launch_status();
+    if (st) return st;
+    vm_launch_pdl(dm_chunk_carry_kernel<C>, dim3(B, H, (Dk * Dv + 255) / 256), dim3(256), 0, stream, dS, (const float*)decay_all, state, state_stride,
+                  state_offset, cu_tokens, slots, H, Dk, Dv);
+    st = vm_launch_status();
+    if (st) return st;
+    vm_launch_pdl(dm_chunk_finish_kernel<C>, dim3(n_chunks, H, (Dv + VS - 1) / VS), dim3(DMC_THREADS), finish, stream, (const float*)q_decayed, (const float*)dS,
+                  cu_tokens, B, o, H, Dk, Dv, VS);
+    return vm_launch_status();
+}
+
+// The same recurrence for prompts, chunk by chunk (three launches).  n_chunks: the step's chunks, sum over its sequences of
+// ceil(tokens / vm_decayed_memory_chunk_tokens(Dk, Dv)); scratch: vm_decayed_memory_scratch_floats(...) float32 words.
+VM_API int vm_decayed_memory_chunked(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau,
+                                     const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale,
+                                     float* state, long long state_stride, int state_offset, const int* positions, const int* cu_tokens, const int* slots,
+                                     float* o, float* scratch, int n_chunks, int T, int B, int H, int Dk, int Dv, cudaStream_t stream) {
+    if (T <= 0 || B <= 0 || n_chunks <= 0) return 0;
+    if (H <= 0 || Dk <= 0 || Dv <= 0 || !state || !scratch || (!z && !head_log_decay) || (z && !(tau > 0.f))) return VM_ERR_BAD_ARG;
+    if (inv_freq && (rotary_dim < 0 || rotary_dim > Dk || rotary_dim % 2)) return VM_ERR_BAD_ARG;
+    const int C = dm_chunk_tokens(Dk, Dv);
+    const float inv_tau = z ? 1.0f / tau : 0.f;
+#define DMC(CC)                                                                                                                                        \
+    return dm_launch_chunks<CC>(proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, head_log_decay, inv_freq, rotary_dim, pairing, q_scale, k_scale, state, \
+                                state_stride, state_offset, positions, cu_tokens, slots, o, scratch, n_chunks, B, H, Dk, Dv, stream)
+    if (C == 64) DMC(64);
+    if (C == 32) DMC(32);
+    if (C == 16) DMC(16);
+#undef DMC
+    return VM_ERR_UNSUPPORTED;
+}
+
 // ------------------------------------------------------------------------------------------------ the output stage
 // out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * silu(g[t, h, :]); a warp per (token, head); w float32 [Dv] or null; g float32 rows of stride ldg
 template <typename T>

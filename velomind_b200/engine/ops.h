@@ -502,9 +502,25 @@ struct MemoryArgs {
     float q_scale = 1.f, k_scale = 1.f;
     int H = 0, Dk = 0, Dv = 0;
 };
+constexpr int MEMORY_CHUNKS_FROM_TOKENS = 64;   // a step's capacity from which prompts run chunk by chunk
 inline void decayed_memory(const float* proj, int ld, const MemoryArgs& a, StepContext& ctx, float* o) {
     Timed t("decayed_memory", ctx.stream);
     need_state(ctx, static_cast<long long>(a.H) * a.Dk * a.Dv, "decayed_memory");
+    // The choice follows the step's capacity bucket alone, so that every step of a bucket asks for the same scratch: decode steps and
+    // the smallest pieces go token by token, everything else chunk by chunk (every sequence may end in a chunk that is not full).
+    const int C = vm_decayed_memory_chunk_tokens(a.Dk, a.Dv);
+    if (C > 0 && !ctx.one_token_each && ctx.T_cap >= MEMORY_CHUNKS_FROM_TOKENS) {
+        float* scratch = static_cast<float*>(ctx.take(vm_decayed_memory_scratch_floats(ctx.T_cap, ctx.B_cap, a.H, a.Dk, a.Dv), DType::F32));
+        int n_chunks = 0;
+        for (int b = 0; b < ctx.B; ++b) n_chunks += (ctx.host_cu_tokens[b + 1] - ctx.host_cu_tokens[b] + C - 1) / C;
+        check(vm_decayed_memory_chunked(proj, ld, a.q_off, a.k_off, a.v_off, a.z, a.ldz, a.tau, a.head_log_decay, a.rot.inv_freq, a.rot.rotary_dim,
+                                        a.rot.pairing, a.q_scale, a.k_scale, ctx.state(), ctx.state_floats(), ctx.state_offset, ctx.positions, ctx.cu_tokens,
+                                        ctx.slots, o, scratch, n_chunks, ctx.T, ctx.B, a.H, a.Dk, a.Dv, ctx.stream),
+              "decayed_memory", ctx.stream);
+        counters().own_launches += 2;       // three kernels
+        ctx.give(scratch);
+        return;
+    }
     check(vm_decayed_memory(proj, ld, a.q_off, a.k_off, a.v_off, a.z, a.ldz, a.tau, a.head_log_decay, a.rot.inv_freq, a.rot.rotary_dim, a.rot.pairing,
                             a.q_scale, a.k_scale, ctx.state(), ctx.state_floats(), ctx.state_offset, ctx.positions, ctx.cu_tokens, ctx.slots, o, ctx.T, ctx.B,
                             a.H, a.Dk, a.Dv, ctx.stream),
