@@ -14,10 +14,10 @@ constexpr int DM_WARPS = 8;          // a warp owns a band of key channels, a la
 constexpr int DM_COLS = 32;
 
 // log(a) of key channel i of head h at token t
-__device__ __forceinline__ float dm_log_decay(const float* __restrict__ head_log_decay, const float* __restrict__ z, int ldz, float inv_tau, size_t t,
-                                              int h, int Dk, int i) {
+__device__ __forceinline__ float dm_log_decay(const float* __restrict__ head_log_decay, const float* __restrict__ z, int ldz, float inv_tau,
+                                              const float* __restrict__ z_bias, size_t t, int h, int Dk, int i) {
     if (!z) return head_log_decay[h];
-    const float x = z[t * ldz + (size_t)h * Dk + i];
+    const float x = z[t * ldz + (size_t)h * Dk + i] + (z_bias ? z_bias[(size_t)h * Dk + i] : 0.f);
     // log sigmoid(x) = -softplus(-x), stable on both sides
     const float ls = x >= 0.f ? -log1pf(expf(-x)) : x - log1pf(expf(x));
     return ls * inv_tau;
@@ -40,7 +40,7 @@ __device__ __forceinline__ float dm_turned(const float* __restrict__ x, int i, i
 // The block walks its sequence's tokens of the step in order; thread (warp w, lane l) keeps S[w NR .. w NR + NR, column l] in registers.
 template <int NR>
 __global__ void __launch_bounds__(DM_WARPS * 32)
-decayed_memory_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ z, int ldz, float inv_tau,
+decayed_memory_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ z, int ldz, float inv_tau, const float* __restrict__ z_bias,
                            const float* __restrict__ head_log_decay, const float* __restrict__ inv_freq, int rotary_dim, int pairing, float q_scale,
                            float k_scale, float* __restrict__ state, long long state_stride, int state_offset, const int* __restrict__ positions,
                            const int* __restrict__ cu_tokens, const int* __restrict__ slots, float* __restrict__ o, int H, int Dk, int Dv) {
@@ -71,7 +71,7 @@ decayed_memory_scan_kernel(const float* __restrict__ proj, int ld, int q_off, in
         for (int i = threadIdx.x; i < Dk; i += blockDim.x) {
             qs[i] = dm_turned(row + q_off + (size_t)h * Dk, i, pos, inv_freq, rotary_dim, pairing) * q_scale;
             ks[i] = dm_turned(row + k_off + (size_t)h * Dk, i, pos, inv_freq, rotary_dim, pairing) * k_scale;
-            as[i] = expf(dm_log_decay(head_log_decay, z, ldz, inv_tau, t, h, Dk, i));
+            as[i] = expf(dm_log_decay(head_log_decay, z, ldz, inv_tau, z_bias, t, h, Dk, i));
         }
         __syncthreads();
         const float v = live ? row[v_off + (size_t)h * Dv + col] : 0.f;
@@ -103,8 +103,8 @@ decayed_memory_scan_kernel(const float* __restrict__ proj, int ld, int q_off, in
 // proj float32 [T, ld] with the queries at column q_off ([H, Dk]), the keys at k_off ([H, Dk]) and the values at v_off ([H, Dv]);
 // z float32 [T, ldz] logits of the decay ([H, Dk]) with tau, or null and head_log_decay float32 [H] (log of the fixed decay);
 // inv_freq [rotary_dim / 2] or null; state [slot, state_stride] float32 with this mixer's [H, Dk, Dv] at state_offset; o float32 [T, H Dv].
-VM_API int vm_decayed_memory(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* head_log_decay,
-                             const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
+VM_API int vm_decayed_memory(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* z_bias,
+                             const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
                              int state_offset, const int* positions, const int* cu_tokens, const int* slots, float* o, int T, int B, int H, int Dk, int Dv,
                              cudaStream_t stream) {
     if (T <= 0 || B <= 0) return 0;
@@ -115,7 +115,7 @@ VM_API int vm_decayed_memory(const float* proj, int ld, int q_off, int k_off, in
     const size_t smem = (size_t)(3 * Dk + DM_WARPS * DM_COLS) * sizeof(float);
     const float inv_tau = z ? 1.0f / tau : 0.f;
 #define DM_LAUNCH(NR)                                                                                                                             \
-    vm_launch_pdl(decayed_memory_scan_kernel<NR>, grid, block, smem, stream, proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, head_log_decay, inv_freq, \
+    vm_launch_pdl(decayed_memory_scan_kernel<NR>, grid, block, smem, stream, proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, z_bias, head_log_decay, inv_freq, \
                   rotary_dim, pairing, q_scale, k_scale, state, state_stride, state_offset, positions, cu_tokens, slots, o, H, Dk, Dv)
     const int per = (Dk + DM_WARPS - 1) / DM_WARPS;
     if (per <= 4) DM_LAUNCH(4);
@@ -157,7 +157,7 @@ __device__ __forceinline__ bool dm_chunk_of(int chunk, const int* __restrict__ c
 // v [C][Dv], A [C][C].  Dk and Dv are multiples of 4.
 template <int C>
 __global__ void __launch_bounds__(DMC_THREADS)
-dm_chunk_local_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ z, int ldz, float inv_tau,
+dm_chunk_local_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ z, int ldz, float inv_tau, const float* __restrict__ z_bias,
                       const float* __restrict__ head_log_decay, const float* __restrict__ inv_freq, int rotary_dim, int pairing, float q_scale,
                       float k_scale, const int* __restrict__ positions, const int* __restrict__ cu_tokens, int B, float* __restrict__ o,
                       float* __restrict__ dS, float* __restrict__ decay_all, float* __restrict__ q_decayed, int H, int Dk, int Dv) {
@@ -184,7 +184,7 @@ dm_chunk_local_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
             const int pos = positions[tok];
             q = dm_turned(row + q_off + (size_t)h * Dk, i, pos, inv_freq, rotary_dim, pairing) * q_scale;
             k = dm_turned(row + k_off + (size_t)h * Dk, i, pos, inv_freq, rotary_dim, pairing) * k_scale;
-            l = dm_log_decay(head_log_decay, z, ldz, inv_tau, tok, h, Dk, i);
+            l = dm_log_decay(head_log_decay, z, ldz, inv_tau, z_bias, tok, h, Dk, i);
         }
         qT[i * CP + t] = q;
         kT[i * CP + t] = k;
@@ -382,8 +382,8 @@ VM_API long long vm_decayed_memory_scratch_floats(int T, int B, int H, int Dk, i
 }
 
 template <int C>
-static int dm_launch_chunks(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float inv_tau, const float* head_log_decay,
-                            const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
+static int dm_launch_chunks(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float inv_tau, const float* z_bias,
+                            const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
                             int state_offset, const int* positions, const int* cu_tokens, const int* slots, float* o, float* scratch, int n_chunks, int B,
                             int H, int Dk, int Dv, cudaStream_t stream) {
     float* dS = scratch;
@@ -395,7 +395,7 @@ static int dm_launch_chunks(const float* proj, int ld, int q_off, int k_off, int
     cudaError_t e = cudaFuncSetAttribute(dm_chunk_local_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)local);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(dm_chunk_finish_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)finish);
     if (e != cudaSuccess) return (int)e;
-    vm_launch_pdl(dm_chunk_local_kernel<C>, dim3(n_chunks, H), dim3(DMC_THREADS), local, stream, proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, head_log_decay,
+    vm_launch_pdl(dm_chunk_local_kernel<C>, dim3(n_chunks, H), dim3(DMC_THREADS), local, stream, proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, z_bias, head_log_decay,
                   inv_freq, rotary_dim, pairing, q_scale, k_scale, positions, cu_tokens, B, o, dS, decay_all, q_decayed, H, Dk, Dv);
     int st = vm_launch_status();
     if (st) return st;
@@ -410,7 +410,7 @@ static int dm_launch_chunks(const float* proj, int ld, int q_off, int k_off, int
 
 // The same recurrence for prompts, chunk by chunk (three launches).  n_chunks: the step's chunks, sum over its sequences of
 // ceil(tokens / vm_decayed_memory_chunk_tokens(Dk, Dv)); scratch: vm_decayed_memory_scratch_floats(...) float32 words.
-VM_API int vm_decayed_memory_chunked(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau,
+VM_API int vm_decayed_memory_chunked(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* z_bias,
                                      const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale,
                                      float* state, long long state_stride, int state_offset, const int* positions, const int* cu_tokens, const int* slots,
                                      float* o, float* scratch, int n_chunks, int T, int B, int H, int Dk, int Dv, cudaStream_t stream) {
@@ -420,7 +420,7 @@ VM_API int vm_decayed_memory_chunked(const float* proj, int ld, int q_off, int k
     const int C = dm_chunk_tokens(Dk, Dv);
     const float inv_tau = z ? 1.0f / tau : 0.f;
 #define DMC(CC)                                                                                                                                        \
-    return dm_launch_chunks<CC>(proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, head_log_decay, inv_freq, rotary_dim, pairing, q_scale, k_scale, state, \
+    return dm_launch_chunks<CC>(proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, z_bias, head_log_decay, inv_freq, rotary_dim, pairing, q_scale, k_scale, state, \
                                 state_stride, state_offset, positions, cu_tokens, slots, o, scratch, n_chunks, B, H, Dk, Dv, stream)
     if (C == 64) DMC(64);
     if (C == 32) DMC(32);

@@ -66,11 +66,110 @@ __global__ void streams_step_kernel(float* __restrict__ h, long long stride, int
     for (int i = threadIdx.x; i < hid; i += blockDim.x) out[t * hid + i] = vm_from_float<T>(urow[i] * inv * norm_w[i]);
 }
 
+// four neighbouring values of a row in the activation dtype, as float32 and back
+__device__ __forceinline__ float4 hc_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 hc_load4(const __nv_bfloat16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void hc_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void hc_store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<const unsigned*>(&a);
+    r.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+// The same for widths that are multiples of 4 up to 4,096: a thread takes up to four runs of four neighbouring values, fetches every copy's
+// run with one 16-byte load (all of them in flight before the first sum) and keeps what the norm needs in registers.
+constexpr int HC_VEC_THREADS = 256, HC_VEC_RUNS = 4;
+template <typename T>
+__global__ void __launch_bounds__(HC_VEC_THREADS)
+streams_step_vec_kernel(float* __restrict__ h, long long stride, int S, const T* __restrict__ y, const float* __restrict__ mix,
+                        const float* __restrict__ w_out, const float* __restrict__ w_in, const float* __restrict__ norm_w, float eps,
+                        T* __restrict__ out, int hid) {
+    __shared__ float red[32];
+    __shared__ float cm[HC_MAX_STREAMS * HC_MAX_STREAMS], co[HC_MAX_STREAMS], ci[HC_MAX_STREAMS];
+    if (threadIdx.x < S * S && y) cm[threadIdx.x] = mix[threadIdx.x];
+    if (threadIdx.x < S) {
+        if (y) co[threadIdx.x] = w_out[threadIdx.x];
+        if (out) ci[threadIdx.x] = w_in[threadIdx.x];
+    }
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    __syncthreads();
+    const size_t t = blockIdx.x;
+    float4 u[HC_VEC_RUNS];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < HC_VEC_RUNS; ++c) {
+        const int i = (threadIdx.x + c * HC_VEC_THREADS) * 4;
+        u[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i >= hid) continue;
+        float4 x[HC_MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            if (s < S) x[s] = *reinterpret_cast<const float4*>(h + s * stride + t * hid + i);
+        if (y) {
+            const float4 yv = hc_load4(y + t * hid + i);
+            float4 nx[HC_MAX_STREAMS];
+#pragma unroll
+            for (int to = 0; to < HC_MAX_STREAMS; ++to)
+                if (to < S) {
+                    float4 a = make_float4(co[to] * yv.x, co[to] * yv.y, co[to] * yv.z, co[to] * yv.w);
+#pragma unroll
+                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                        if (s < S) {
+                            const float m = cm[s * S + to];
+                            a.x = fmaf(m, x[s].x, a.x); a.y = fmaf(m, x[s].y, a.y); a.z = fmaf(m, x[s].z, a.z); a.w = fmaf(m, x[s].w, a.w);
+                        }
+                    nx[to] = a;
+                }
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                if (s < S) {
+                    x[s] = nx[s];
+                    *reinterpret_cast<float4*>(h + s * stride + t * hid + i) = nx[s];
+                }
+        }
+        if (out) {
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                if (s < S) { a.x = fmaf(ci[s], x[s].x, a.x); a.y = fmaf(ci[s], x[s].y, a.y); a.z = fmaf(ci[s], x[s].z, a.z); a.w = fmaf(ci[s], x[s].w, a.w); }
+            u[c] = a;
+            ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+        }
+    }
+    if (!out) return;
+    ss = vm_block_sum(ss, red);
+    const float inv = 1.0f / sqrtf(ss / (float)hid + eps);
+#pragma unroll
+    for (int c = 0; c < HC_VEC_RUNS; ++c) {
+        const int i = (threadIdx.x + c * HC_VEC_THREADS) * 4;
+        if (i >= hid) continue;
+        const float4 w = *reinterpret_cast<const float4*>(norm_w + i);
+        hc_store4(out + t * hid + i, make_float4(u[c].x * inv * w.x, u[c].y * inv * w.y, u[c].z * inv * w.z, u[c].w * inv * w.w));
+    }
+}
+
 VM_API int vm_streams_step(float* h, long long stride, int S, const void* y, const float* mix, const float* w_out, const float* w_in,
                            const float* norm_w, float eps, void* out, int T, int hid, int act_dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (S < 1 || S > HC_MAX_STREAMS) return VM_ERR_UNSUPPORTED;
     if (hid <= 0 || (y && (!mix || !w_out)) || (out && (!w_in || !norm_w)) || (!y && !out)) return VM_ERR_BAD_ARG;
+    if (act_dtype != VM_F32 && act_dtype != VM_BF16) return VM_ERR_UNSUPPORTED;
+    if (hid % 4 == 0 && hid >= 128 && hid <= 4 * HC_VEC_THREADS * HC_VEC_RUNS && stride % 4 == 0) {
+        if (act_dtype == VM_F32)
+            vm_launch_pdl(streams_step_vec_kernel<float>, dim3(T), dim3(HC_VEC_THREADS), 0, stream, h, stride, S, (const float*)y, mix, w_out, w_in, norm_w,
+                          eps, (float*)out, hid);
+        else
+            vm_launch_pdl(streams_step_vec_kernel<__nv_bfloat16>, dim3(T), dim3(HC_VEC_THREADS), 0, stream, h, stride, S, (const __nv_bfloat16*)y, mix, w_out,
+                          w_in, norm_w, eps, (__nv_bfloat16*)out, hid);
+        return vm_launch_status();
+    }
     const size_t smem = (size_t)hid * sizeof(float);
     if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
     const int threads = hid >= 1024 ? 256 : 128;

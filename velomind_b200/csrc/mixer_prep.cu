@@ -234,11 +234,90 @@ __global__ void join_rows_kernel(const T* __restrict__ a, const T* __restrict__ 
     }
 }
 
+__device__ __forceinline__ float4 jr_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 jr_load4(const __nv_bfloat16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void jr_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void jr_store4(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<const unsigned*>(&a);
+    r.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+// the same for rows of 4 n values up to 4,096: every thread keeps up to four runs of four values of both rows in registers
+constexpr int JR_THREADS = 256, JR_RUNS = 4;
+template <typename T>
+__global__ void __launch_bounds__(JR_THREADS)
+join_rows_vec_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ bias_a, float ca, float cb,
+                     const float* __restrict__ wa, const float* __restrict__ wb, float eps, T* __restrict__ out, int cols) {
+    __shared__ float red[32];
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const size_t t = blockIdx.x;
+    float4 x[JR_RUNS], y[JR_RUNS];
+    float sa = 0.f, sb = 0.f;
+#pragma unroll
+    for (int c = 0; c < JR_RUNS; ++c) {
+        const int i = (threadIdx.x + c * JR_THREADS) * 4;
+        x[c] = y[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i >= cols) continue;
+        x[c] = jr_load4(a + t * cols + i);
+        if (bias_a) {
+            const float4 bb = *reinterpret_cast<const float4*>(bias_a + i);
+            x[c].x += bb.x; x[c].y += bb.y; x[c].z += bb.z; x[c].w += bb.w;
+        }
+        if (b) y[c] = jr_load4(b + t * cols + i);
+        sa += x[c].x * x[c].x + x[c].y * x[c].y + x[c].z * x[c].z + x[c].w * x[c].w;
+        sb += y[c].x * y[c].x + y[c].y * y[c].y + y[c].z * y[c].z + y[c].w * y[c].w;
+    }
+    float ia = ca, ib = cb;
+    if (wa) {
+        sa = vm_block_sum(sa, red);
+        sb = vm_block_sum(sb, red);
+        ia = ca / sqrtf(sa / (float)cols + eps);
+        ib = cb / sqrtf(sb / (float)cols + eps);
+    }
+#pragma unroll
+    for (int c = 0; c < JR_RUNS; ++c) {
+        const int i = (threadIdx.x + c * JR_THREADS) * 4;
+        if (i >= cols) continue;
+        float4 r = make_float4(x[c].x * ia, x[c].y * ia, x[c].z * ia, x[c].w * ia);
+        if (wa) {
+            const float4 w = *reinterpret_cast<const float4*>(wa + i);
+            r.x *= w.x; r.y *= w.y; r.z *= w.z; r.w *= w.w;
+        }
+        if (b) {
+            float4 q = make_float4(y[c].x * ib, y[c].y * ib, y[c].z * ib, y[c].w * ib);
+            if (wb) {
+                const float4 w = *reinterpret_cast<const float4*>(wb + i);
+                q.x *= w.x; q.y *= w.y; q.z *= w.z; q.w *= w.w;
+            }
+            r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w;
+        }
+        jr_store4(out + t * cols + i, r);
+    }
+}
+
 // b null: out = ca * (a + bias_a) alone (a bias on rows, in place if out == a)
 VM_API int vm_join_rows(const void* a, const void* b, const float* bias_a, float ca, float cb, const float* wa, const float* wb, float eps, void* out,
                         int T, int cols, int act_dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (cols <= 0 || (b && (wa != nullptr) != (wb != nullptr))) return VM_ERR_BAD_ARG;
+    if (act_dtype != VM_F32 && act_dtype != VM_BF16) return VM_ERR_UNSUPPORTED;
+    if (cols % 4 == 0 && cols >= 128 && cols <= 4 * JR_THREADS * JR_RUNS) {
+        if (act_dtype == VM_F32)
+            vm_launch_pdl(join_rows_vec_kernel<float>, dim3(T), dim3(JR_THREADS), 0, stream, (const float*)a, (const float*)b, bias_a, ca, cb, wa, wb, eps,
+                          (float*)out, cols);
+        else
+            vm_launch_pdl(join_rows_vec_kernel<__nv_bfloat16>, dim3(T), dim3(JR_THREADS), 0, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, bias_a, ca,
+                          cb, wa, wb, eps, (__nv_bfloat16*)out, cols);
+        return vm_launch_status();
+    }
     const int threads = cols >= 1024 ? 256 : 128;
     if (act_dtype == VM_F32)
         vm_launch_pdl(join_rows_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)a, (const float*)b, bias_a, ca, cb, wa, wb, eps, (float*)out,

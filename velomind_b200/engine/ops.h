@@ -497,6 +497,7 @@ struct MemoryArgs {
     const float* z = nullptr;           // decay logits float32 [T, ldz], or null: head_log_decay
     int ldz = 0;
     float tau = 1.f;
+    const float* z_bias = nullptr;      // float32 [H, Dk] added to the logits, or null
     const float* head_log_decay = nullptr;
     RotaryTable rot;
     float q_scale = 1.f, k_scale = 1.f;
@@ -513,7 +514,7 @@ inline void decayed_memory(const float* proj, int ld, const MemoryArgs& a, StepC
         float* scratch = static_cast<float*>(ctx.take(vm_decayed_memory_scratch_floats(ctx.T_cap, ctx.B_cap, a.H, a.Dk, a.Dv), DType::F32));
         int n_chunks = 0;
         for (int b = 0; b < ctx.B; ++b) n_chunks += (ctx.host_cu_tokens[b + 1] - ctx.host_cu_tokens[b] + C - 1) / C;
-        check(vm_decayed_memory_chunked(proj, ld, a.q_off, a.k_off, a.v_off, a.z, a.ldz, a.tau, a.head_log_decay, a.rot.inv_freq, a.rot.rotary_dim,
+        check(vm_decayed_memory_chunked(proj, ld, a.q_off, a.k_off, a.v_off, a.z, a.ldz, a.tau, a.z_bias, a.head_log_decay, a.rot.inv_freq, a.rot.rotary_dim,
                                         a.rot.pairing, a.q_scale, a.k_scale, ctx.state(), ctx.state_floats(), ctx.state_offset, ctx.positions, ctx.cu_tokens,
                                         ctx.slots, o, scratch, n_chunks, ctx.T, ctx.B, a.H, a.Dk, a.Dv, ctx.stream),
               "decayed_memory", ctx.stream);
@@ -521,7 +522,7 @@ inline void decayed_memory(const float* proj, int ld, const MemoryArgs& a, StepC
         ctx.give(scratch);
         return;
     }
-    check(vm_decayed_memory(proj, ld, a.q_off, a.k_off, a.v_off, a.z, a.ldz, a.tau, a.head_log_decay, a.rot.inv_freq, a.rot.rotary_dim, a.rot.pairing,
+    check(vm_decayed_memory(proj, ld, a.q_off, a.k_off, a.v_off, a.z, a.ldz, a.tau, a.z_bias, a.head_log_decay, a.rot.inv_freq, a.rot.rotary_dim, a.rot.pairing,
                             a.q_scale, a.k_scale, ctx.state(), ctx.state_floats(), ctx.state_offset, ctx.positions, ctx.cu_tokens, ctx.slots, o, ctx.T, ctx.B,
                             a.H, a.Dk, a.Dv, ctx.stream),
           "decayed_memory", ctx.stream);

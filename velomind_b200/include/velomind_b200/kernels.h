@@ -292,17 +292,17 @@ int vm_join_rows(const void* a, const void* b, const float* bias_a, float ca, fl
 
 // ---- decayed_memory.cu: linear attention with a decaying matrix memory S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t
 // proj float32 [T, ld] with queries at q_off ([H, Dk]), keys at k_off, values at v_off ([H, Dv]); z float32 [T, ldz] decay logits
-// (a = sigmoid(z)^(1 / tau)) or null with head_log_decay float32 [H]; inv_freq or null; the [H, Dk, Dv] memory of a sequence lies in
+// (a = sigmoid(z + z_bias)^(1 / tau), z_bias float32 [H, Dk] or null) or null with head_log_decay float32 [H]; inv_freq or null; the [H, Dk, Dv] memory of a sequence lies in
 // state [slot, state_stride] at state_offset; o float32 [T, H Dv]
-int vm_decayed_memory(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* head_log_decay,
-                      const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
+int vm_decayed_memory(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* z_bias,
+                      const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
                       int state_offset, const int* positions, const int* cu_tokens, const int* slots, float* o, int T, int B, int H, int Dk, int Dv,
                       cudaStream_t stream);
 // the same for prompts, chunk by chunk in three launches (keys and values in multiples of 4 that fit the shared memory: the chunk's
 // tokens, 64 / 32 / 16, or 0 where the sizes are not taken); n_chunks: sum over the step's sequences of ceil(tokens / chunk tokens)
 int vm_decayed_memory_chunk_tokens(int Dk, int Dv);
 long long vm_decayed_memory_scratch_floats(int T, int B, int H, int Dk, int Dv);
-int vm_decayed_memory_chunked(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau,
+int vm_decayed_memory_chunked(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* z_bias,
                               const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale,
                               float* state, long long state_stride, int state_offset, const int* positions, const int* cu_tokens, const int* slots,
                               float* o, float* scratch, int n_chunks, int T, int B, int H, int Dk, int Dv, cudaStream_t stream);

@@ -111,7 +111,6 @@ public:
             z = static_cast<float*>(ctx.take_tokens(nqk, DType::F32));
             a2_.apply(ctx, low, DType::F32, z, DType::F32, ctx.T, ctx.T_cap);
             ctx.give(low);
-            ops::join_rows(z, nullptr, static_cast<const float*>(a2b_.ptr), 1.f, 0.f, nullptr, nullptr, 0.f, z, ctx.T, static_cast<int>(nqk), DType::F32, ctx.stream);
         }
         ops::MemoryArgs m;
         m.q_off = 0;
@@ -120,6 +119,7 @@ public:
         m.z = z;
         m.ldz = static_cast<int>(nqk);
         m.tau = tau_;
+        m.z_bias = channel_ ? static_cast<const float*>(a2b_.ptr) : nullptr;      // (the second product's bias rides in the recurrence kernel)
         m.head_log_decay = channel_ ? nullptr : static_cast<const float*>(log_decay_dev_.ptr);
         m.rot = rotary_;
         m.q_scale = q_scale_;
@@ -134,7 +134,7 @@ public:
         ops::memory_output(o, proj + 2 * nqk + nv, ld, norm_weight_ ? static_cast<const float*>(norm_.ptr) : nullptr, eps_, gated, ctx.T, H_, Dv_, act, ctx.stream);
         ctx.give(o);
         ctx.give(proj);
-        out_.apply(ctx, gated, act, out, act, ctx.T, ctx.T_cap);
+        project(ctx, out_, gated, out);
         ctx.give(gated);
     }
 

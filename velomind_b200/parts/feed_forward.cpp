@@ -81,6 +81,15 @@ public:
     }
 
     void forward(StepContext& ctx, const void* x, void* out) override {
+        // few rows in bfloat16 (a layer whose wiring adds the result itself): the weight-streaming kernels, without norm or sum
+        if (ctx.act_dtype == DType::BF16 && gate_up_.weight.dtype == DType::BF16 && down_.weight.dtype == DType::BF16 && ctx.T_cap <= max_rows() &&
+            hidden_ % 32 == 0 && I_ % 32 == 0 && ctx.T > 0) {
+            void* act = ctx.take_tokens(I_, DType::BF16);
+            ops::skinny_gated(x, nullptr, 0.f, gate_up_.weight, ctx.T, I_, act_, act, ctx.err, ctx.stream);
+            ops::skinny_linear(act, nullptr, 0.f, down_.weight, ctx.T, out, hidden_, false, nullptr, ctx.err, ctx.stream);
+            ctx.give(act);
+            return;
+        }
         void* gu = ctx.take_tokens(2ll * I_, ctx.act_dtype);
         gate_up_.apply(ctx, x, ctx.act_dtype, gu, ctx.act_dtype, ctx.T, ctx.T_cap);
         void* act = ctx.take_tokens(I_, ctx.act_dtype);

@@ -152,7 +152,7 @@ public:
         if (gate_cols_ && gate_per_ == 1) ops::sigmoid_gate(att, proj + row_cols(), ld, ctx.T, H_ * Dv_, act, ctx.stream);
         else if (gate_cols_) ops::sigmoid_gate_heads(att, proj + row_cols(), ld, ctx.T, H_ * Dv_, gate_per_, act, ctx.stream);
         ctx.give(proj);
-        out_.apply(ctx, att, act, out, act, ctx.T, ctx.T_cap);
+        project(ctx, out_, att, out);
         ctx.give(att);
         if (out_bias_) ops::join_rows(out, nullptr, static_cast<const float*>(ob_.ptr), 1.f, 0.f, nullptr, nullptr, 0.f, out, ctx.T, hidden_, act, ctx.stream);
     }

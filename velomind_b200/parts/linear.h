@@ -55,4 +55,14 @@ inline void project_f32(StepContext& ctx, const Linear& lin, const void* x, floa
         lin.apply(ctx, x, ctx.act_dtype, out, DType::F32, ctx.T, ctx.T_cap);
 }
 
+// out [rows, N] in the activation dtype = x W^T, chosen the same way
+inline void project(StepContext& ctx, const Linear& lin, const void* x, void* out) {
+    const DeviceTensor& W = lin.weight;
+    if (ctx.act_dtype == DType::BF16 && W.dtype == DType::BF16 && lin.out_features % 8 == 0 && ops::skinny_ok(ctx.T, lin.in_features, W) &&
+        ctx.T_cap <= ops::skinny_max_rows(2 * W.rows() * W.cols()))
+        ops::skinny_linear(x, nullptr, 0.f, W, ctx.T, out, static_cast<int>(lin.out_features), false, nullptr, ctx.err, ctx.stream);
+    else
+        lin.apply(ctx, x, ctx.act_dtype, out, ctx.act_dtype, ctx.T, ctx.T_cap);
+}
+
 }  // namespace vmb
