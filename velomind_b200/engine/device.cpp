@@ -187,6 +187,14 @@ DType BindContext::matrix_dtype(const std::vector<const HostTensor*>& stored) co
 // ------------------------------------------------------------------------------------------------ launch bookkeeping
 namespace ops {
 
+bool memory_scan_forced() {
+    static const bool on = [] {
+        const char* s = std::getenv("VELOMIND_B200_MEMORY_SCAN");
+        return s && *s && *s != '0';
+    }();
+    return on;
+}
+
 int SKINNY_MAX_ROWS = 32;      // beyond this the library product wins (the A tile is staged once per CTA; measured per decode step at
                                // 33 / 48 / 64 rows: 1.07 / 1.20 / 1.25 ms fused against 1.02 / 1.07 / 1.05 ms with the library product)
 // Large weight matrices: the library product streams them at 3.5 to 5.5 TB/s from 16 rows on, whatever the row count (hidden

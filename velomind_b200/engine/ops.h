@@ -503,6 +503,7 @@ struct MemoryArgs {
     float q_scale = 1.f, k_scale = 1.f;
     int H = 0, Dk = 0, Dv = 0;
 };
+bool memory_scan_forced();                      // debugging aid: VELOMIND_B200_MEMORY_SCAN=1 keeps prompts on the token-by-token kernel
 constexpr int MEMORY_CHUNKS_FROM_TOKENS = 64;   // a step's capacity from which prompts run chunk by chunk
 inline void decayed_memory(const float* proj, int ld, const MemoryArgs& a, StepContext& ctx, float* o) {
     Timed t("decayed_memory", ctx.stream);
@@ -510,7 +511,7 @@ inline void decayed_memory(const float* proj, int ld, const MemoryArgs& a, StepC
     // The choice follows the step's capacity bucket alone, so that every step of a bucket asks for the same scratch: decode steps and
     // the smallest pieces go token by token, everything else chunk by chunk (every sequence may end in a chunk that is not full).
     const int C = vm_decayed_memory_chunk_tokens(a.Dk, a.Dv);
-    if (C > 0 && !ctx.one_token_each && ctx.T_cap >= MEMORY_CHUNKS_FROM_TOKENS) {
+    if (C > 0 && !ctx.one_token_each && ctx.T_cap >= MEMORY_CHUNKS_FROM_TOKENS && !memory_scan_forced()) {
         float* scratch = static_cast<float*>(ctx.take(vm_decayed_memory_scratch_floats(ctx.T_cap, ctx.B_cap, a.H, a.Dk, a.Dv), DType::F32));
         int n_chunks = 0;
         for (int b = 0; b < ctx.B; ++b) n_chunks += (ctx.host_cu_tokens[b + 1] - ctx.host_cu_tokens[b] + C - 1) / C;
