@@ -307,11 +307,22 @@ __global__ void dm_chunk_carry_kernel(float* __restrict__ dS, const float* __res
     float* S = state + (size_t)slots[seq] * state_stride + state_offset + (size_t)h * Dk * Dv + e;
     float cur = *S;
     const int i = e / Dv;
-    for (int c = 0; c < nc; ++c) {
-        const size_t ch = (size_t)(first + c) * H + h;
-        const float add = dS[ch * Dk * Dv + e];
-        dS[ch * Dk * Dv + e] = cur;                       // the memory at this chunk's start, for the finish pass
-        cur = fmaf(decay_all[ch * Dk + i], cur, add);
+    // eight chunks' values are fetched before the first store (the compiler cannot move a load over a store into the same array)
+    for (int c0 = 0; c0 < nc; c0 += 8) {
+        float add[8], dec[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const size_t ch = (size_t)(first + min(c0 + j, nc - 1)) * H + h;
+            add[j] = dS[ch * Dk * Dv + e];
+            dec[j] = decay_all[ch * Dk + i];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (c0 + j < nc) {
+                const size_t ch = (size_t)(first + c0 + j) * H + h;
+                dS[ch * Dk * Dv + e] = cur;               // the memory at this chunk's start, for the finish pass
+                cur = fmaf(dec[j], cur, add[j]);
+            }
     }
     *S = cur;
 }
