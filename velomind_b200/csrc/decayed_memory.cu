@@ -153,8 +153,31 @@ __device__ __forceinline__ bool dm_chunk_of(int chunk, const int* __restrict__ c
     return false;
 }
 
+// Rotary positions on the queries and keys of all heads, in place in the float32 projections: the angle of a (token, pair) is computed
+// once and serves every head.  One block per token.
+__global__ void dm_turn_rows_kernel(float* __restrict__ proj, int ld, int q_off, int k_off, const float* __restrict__ inv_freq, int rotary_dim, int pairing,
+                                    const int* __restrict__ positions, int H, int Dk) {
+    vm_pdl_launch_dependents();
+    vm_pdl_wait();
+    const size_t t = blockIdx.x;
+    const int half = rotary_dim / 2;
+    const float pos = (float)positions[t];
+    float* row = proj + t * ld;
+    for (int p = threadIdx.x; p < half; p += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * inv_freq[p], &sn, &cs);
+        const int a = pairing == VM_PAIR_INTERLEAVED ? 2 * p : p, b = pairing == VM_PAIR_INTERLEAVED ? 2 * p + 1 : p + half;
+        for (int h = 0; h < 2 * H; ++h) {
+            float* x = row + (h < H ? q_off + (size_t)h * Dk : k_off + (size_t)(h - H) * Dk);
+            const float u = x[a], v = x[b];
+            x[a] = u * cs - v * sn;
+            x[b] = v * cs + u * sn;
+        }
+    }
+}
+
 // grid (chunks, heads).  Shared: qT, kT, bT [Dk][C + 4] (channel-major, so that four neighbouring tokens are one 16-byte load),
-// v [C][Dv], A [C][C].  Dk and Dv are multiples of 4.
+// v [C][Dv], A [C][C].  Dk and Dv are multiples of 4, and so are ld and the three offsets; q and k come already turned (dm_turn_rows_kernel).
 template <int C>
 __global__ void __launch_bounds__(DMC_THREADS)
 dm_chunk_local_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, const float* __restrict__ z, int ldz, float inv_tau, const float* __restrict__ z_bias,
@@ -174,21 +197,25 @@ dm_chunk_local_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
     if (!dm_chunk_of(blockIdx.x, cu_tokens, B, C, seq, start, len)) return;
     const int h = blockIdx.y, tid = threadIdx.x;
     const bool per_channel = z != nullptr;
-    // a. queries, keys (turned and scaled) and log decays, channel-major; values
-    for (int idx = tid; idx < C * Dk; idx += DMC_THREADS) {
-        const int t = idx / Dk, i = idx - t * Dk;
-        float q = 0.f, k = 0.f, l = 0.f;
+    // a. queries and keys (already turned; scaled here) and log decays, channel-major.  A thread takes four neighbouring channels of a
+    // token with 16-byte loads; neighbouring lanes take neighbouring tokens, so the transposed stores meet no bank twice.
+    (void)inv_freq; (void)rotary_dim; (void)pairing; (void)positions;
+    for (int idx = tid; idx < C * (Dk / 4); idx += DMC_THREADS) {
+        const int t = idx % C, i = (idx / C) * 4;
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f), k = q, l = q;
         if (t < len) {
             const size_t tok = (size_t)start + t;
             const float* row = proj + tok * ld;
-            const int pos = positions[tok];
-            q = dm_turned(row + q_off + (size_t)h * Dk, i, pos, inv_freq, rotary_dim, pairing) * q_scale;
-            k = dm_turned(row + k_off + (size_t)h * Dk, i, pos, inv_freq, rotary_dim, pairing) * k_scale;
-            l = dm_log_decay(head_log_decay, z, ldz, inv_tau, z_bias, tok, h, Dk, i);
+            q = *reinterpret_cast<const float4*>(row + q_off + (size_t)h * Dk + i);
+            k = *reinterpret_cast<const float4*>(row + k_off + (size_t)h * Dk + i);
+            l.x = dm_log_decay(head_log_decay, z, ldz, inv_tau, z_bias, tok, h, Dk, i);
+            l.y = per_channel ? dm_log_decay(head_log_decay, z, ldz, inv_tau, z_bias, tok, h, Dk, i + 1) : l.x;
+            l.z = per_channel ? dm_log_decay(head_log_decay, z, ldz, inv_tau, z_bias, tok, h, Dk, i + 2) : l.x;
+            l.w = per_channel ? dm_log_decay(head_log_decay, z, ldz, inv_tau, z_bias, tok, h, Dk, i + 3) : l.x;
         }
-        qT[i * CP + t] = q;
-        kT[i * CP + t] = k;
-        bT[i * CP + t] = l;
+        qT[(i + 0) * CP + t] = q.x * q_scale; qT[(i + 1) * CP + t] = q.y * q_scale; qT[(i + 2) * CP + t] = q.z * q_scale; qT[(i + 3) * CP + t] = q.w * q_scale;
+        kT[(i + 0) * CP + t] = k.x * k_scale; kT[(i + 1) * CP + t] = k.y * k_scale; kT[(i + 2) * CP + t] = k.z * k_scale; kT[(i + 3) * CP + t] = k.w * k_scale;
+        bT[(i + 0) * CP + t] = l.x; bT[(i + 1) * CP + t] = l.y; bT[(i + 2) * CP + t] = l.z; bT[(i + 3) * CP + t] = l.w;
     }
     for (int idx = tid; idx < C * Dv; idx += DMC_THREADS) {
         const int t = idx / Dv, j = idx - t * Dv;
@@ -204,21 +231,45 @@ dm_chunk_local_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
         }
     }
     __syncthreads();
-    // c. A[t][s] = sum_i q_t[i] k_s[i] exp(b_t[i] - b_s[i]) for s <= t, in tiles of 4 x 4 (tiles wholly above the diagonal are never read)
-    for (int tile = tid; tile < (C / 4) * (C / 4); tile += DMC_THREADS) {
-        const int t0 = (tile / (C / 4)) * 4, s0 = (tile % (C / 4)) * 4;
-        if (s0 > t0 + 3 || t0 >= len) continue;
+    // c. A[t][s] = sum_i q_t[i] k_s[i] exp(b_t[i] - b_s[i]) for s <= t, in tiles of 4 x 4.  Only the tiles on and below the diagonal are
+    // computed (the others are never read): the C / 4 diagonal ones first, so that they share a warp, then the rest row by row.  Below
+    // the diagonal every key of a tile lies before every query of it, and the decay factors through the tile's last key m:
+    // exp(b_t - b_s) = exp(b_t - b_m) exp(b_m - b_s), both exponents <= 0, eight exponentials per channel instead of sixteen.
+    constexpr int NT = C / 4;
+    for (int item = tid; item < NT * (NT + 1) / 2; item += DMC_THREADS) {
+        int tt, st;
+        if (item < NT) { tt = st = item; }
+        else {
+            int r = item - NT;                              // the r-th tile below the diagonal: row tt has tt of them
+            tt = 1;
+            while (r >= tt) { r -= tt; ++tt; }
+            st = r;
+        }
+        const int t0 = tt * 4, s0 = st * 4;
+        if (t0 >= len) continue;
         float acc[4][4] = {};
-        if (per_channel) {
+        if (per_channel && tt == st) {
             for (int i = 0; i < Dk; ++i) {
                 const float4 q4 = *reinterpret_cast<const float4*>(qT + i * CP + t0), k4 = *reinterpret_cast<const float4*>(kT + i * CP + s0);
-                const float4 bt = *reinterpret_cast<const float4*>(bT + i * CP + t0), bs = *reinterpret_cast<const float4*>(bT + i * CP + s0);
-                const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w};
-                const float ba[4] = {bt.x, bt.y, bt.z, bt.w}, bb[4] = {bs.x, bs.y, bs.z, bs.w};
+                const float4 bt = *reinterpret_cast<const float4*>(bT + i * CP + t0);
+                const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w}, ba[4] = {bt.x, bt.y, bt.z, bt.w};
 #pragma unroll
                 for (int a = 0; a < 4; ++a)
 #pragma unroll
-                    for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qa[a] * ka[b], __expf(fminf(ba[a] - bb[b], 0.f)), acc[a][b]);
+                    for (int b = 0; b < 4; ++b)
+                        if (b <= a) acc[a][b] = fmaf(qa[a] * ka[b], __expf(ba[a] - ba[b]), acc[a][b]);
+            }
+        } else if (per_channel) {
+            for (int i = 0; i < Dk; ++i) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qT + i * CP + t0), k4 = *reinterpret_cast<const float4*>(kT + i * CP + s0);
+                const float4 bt = *reinterpret_cast<const float4*>(bT + i * CP + t0), bs = *reinterpret_cast<const float4*>(bT + i * CP + s0);
+                const float m = bs.w;
+                const float qa[4] = {q4.x * __expf(bt.x - m), q4.y * __expf(bt.y - m), q4.z * __expf(bt.z - m), q4.w * __expf(bt.w - m)};
+                const float ka[4] = {k4.x * __expf(m - bs.x), k4.y * __expf(m - bs.y), k4.z * __expf(m - bs.z), k4.w};
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(qa[a], ka[b], acc[a][b]);
             }
         } else {
             for (int i = 0; i < Dk; ++i) {
@@ -393,10 +444,10 @@ VM_API long long vm_decayed_memory_scratch_floats(int T, int B, int H, int Dk, i
 }
 
 template <int C>
-static int dm_launch_chunks(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float inv_tau, const float* z_bias,
+static int dm_launch_chunks(float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float inv_tau, const float* z_bias,
                             const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
-                            int state_offset, const int* positions, const int* cu_tokens, const int* slots, float* o, float* scratch, int n_chunks, int B,
-                            int H, int Dk, int Dv, cudaStream_t stream) {
+                            int state_offset, const int* positions, const int* cu_tokens, const int* slots, float* o, float* scratch, int n_chunks, int T,
+                            int B, int H, int Dk, int Dv, cudaStream_t stream) {
     float* dS = scratch;
     float* decay_all = dS + (size_t)n_chunks * H * Dk * Dv;
     float* q_decayed = decay_all + (size_t)n_chunks * H * Dk;
@@ -406,9 +457,15 @@ static int dm_launch_chunks(const float* proj, int ld, int q_off, int k_off, int
     cudaError_t e = cudaFuncSetAttribute(dm_chunk_local_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)local);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(dm_chunk_finish_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)finish);
     if (e != cudaSuccess) return (int)e;
-    vm_launch_pdl(dm_chunk_local_kernel<C>, dim3(n_chunks, H), dim3(DMC_THREADS), local, stream, proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, z_bias, head_log_decay,
-                  inv_freq, rotary_dim, pairing, q_scale, k_scale, positions, cu_tokens, B, o, dS, decay_all, q_decayed, H, Dk, Dv);
-    int st = vm_launch_status();
+    int st = 0;
+    if (inv_freq && rotary_dim > 0) {              // turn q and k once for all heads; the chunk kernels then read them as they are
+        vm_launch_pdl(dm_turn_rows_kernel, dim3(T), dim3(64), 0, stream, proj, ld, q_off, k_off, inv_freq, rotary_dim, pairing, positions, H, Dk);
+        st = vm_launch_status();
+        if (st) return st;
+    }
+    vm_launch_pdl(dm_chunk_local_kernel<C>, dim3(n_chunks, H), dim3(DMC_THREADS), local, stream, (const float*)proj, ld, q_off, k_off, v_off, z, ldz, inv_tau,
+                  z_bias, head_log_decay, (const float*)nullptr, 0, pairing, q_scale, k_scale, positions, cu_tokens, B, o, dS, decay_all, q_decayed, H, Dk, Dv);
+    st = vm_launch_status();
     if (st) return st;
     vm_launch_pdl(dm_chunk_carry_kernel<C>, dim3(B, H, (Dk * Dv + 255) / 256), dim3(256), 0, stream, dS, (const float*)decay_all, state, state_stride,
                   state_offset, cu_tokens, slots, H, Dk, Dv);
@@ -419,20 +476,21 @@ static int dm_launch_chunks(const float* proj, int ld, int q_off, int k_off, int
     return vm_launch_status();
 }
 
-// The same recurrence for prompts, chunk by chunk (three launches).  n_chunks: the step's chunks, sum over its sequences of
+// The same recurrence for prompts, chunk by chunk (three launches, and one before them that turns the queries and keys of `proj` in place).  n_chunks: the step's chunks, sum over its sequences of
 // ceil(tokens / vm_decayed_memory_chunk_tokens(Dk, Dv)); scratch: vm_decayed_memory_scratch_floats(...) float32 words.
-VM_API int vm_decayed_memory_chunked(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* z_bias,
+VM_API int vm_decayed_memory_chunked(float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* z_bias,
                                      const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale,
                                      float* state, long long state_stride, int state_offset, const int* positions, const int* cu_tokens, const int* slots,
                                      float* o, float* scratch, int n_chunks, int T, int B, int H, int Dk, int Dv, cudaStream_t stream) {
     if (T <= 0 || B <= 0 || n_chunks <= 0) return 0;
     if (H <= 0 || Dk <= 0 || Dv <= 0 || !state || !scratch || (!z && !head_log_decay) || (z && !(tau > 0.f))) return VM_ERR_BAD_ARG;
     if (inv_freq && (rotary_dim < 0 || rotary_dim > Dk || rotary_dim % 2)) return VM_ERR_BAD_ARG;
+    if (ld % 4 || q_off % 4 || k_off % 4 || (z && ldz % 4)) return VM_ERR_BAD_ARG;      // (16-byte loads of a token's queries and keys)
     const int C = dm_chunk_tokens(Dk, Dv);
     const float inv_tau = z ? 1.0f / tau : 0.f;
 #define DMC(CC)                                                                                                                                        \
     return dm_launch_chunks<CC>(proj, ld, q_off, k_off, v_off, z, ldz, inv_tau, z_bias, head_log_decay, inv_freq, rotary_dim, pairing, q_scale, k_scale, state, \
-                                state_stride, state_offset, positions, cu_tokens, slots, o, scratch, n_chunks, B, H, Dk, Dv, stream)
+                                state_stride, state_offset, positions, cu_tokens, slots, o, scratch, n_chunks, T, B, H, Dk, Dv, stream)
     if (C == 64) DMC(64);
     if (C == 32) DMC(32);
     if (C == 16) DMC(16);

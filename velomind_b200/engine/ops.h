@@ -505,7 +505,7 @@ struct MemoryArgs {
 };
 bool memory_scan_forced();                      // debugging aid: VELOMIND_B200_MEMORY_SCAN=1 keeps prompts on the token-by-token kernel
 constexpr int MEMORY_CHUNKS_FROM_TOKENS = 64;   // a step's capacity from which prompts run chunk by chunk
-inline void decayed_memory(const float* proj, int ld, const MemoryArgs& a, StepContext& ctx, float* o) {
+inline void decayed_memory(float* proj, int ld, const MemoryArgs& a, StepContext& ctx, float* o) {      // (prompts: q and k of `proj` are turned in place)
     Timed t("decayed_memory", ctx.stream);
     need_state(ctx, static_cast<long long>(a.H) * a.Dk * a.Dv, "decayed_memory");
     // The choice follows the step's capacity bucket alone, so that every step of a bucket asks for the same scratch: decode steps and
@@ -519,7 +519,7 @@ inline void decayed_memory(const float* proj, int ld, const MemoryArgs& a, StepC
                                         a.rot.pairing, a.q_scale, a.k_scale, ctx.state(), ctx.state_floats(), ctx.state_offset, ctx.positions, ctx.cu_tokens,
                                         ctx.slots, o, scratch, n_chunks, ctx.T, ctx.B, a.H, a.Dk, a.Dv, ctx.stream),
               "decayed_memory", ctx.stream);
-        counters().own_launches += 2;       // three kernels
+        counters().own_launches += a.rot.inv_freq ? 3 : 2;       // three kernels, and one that turns q and k
         ctx.give(scratch);
         return;
     }

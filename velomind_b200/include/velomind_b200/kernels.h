@@ -298,11 +298,11 @@ int vm_decayed_memory(const float* proj, int ld, int q_off, int k_off, int v_off
                       const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale, float* state, long long state_stride,
                       int state_offset, const int* positions, const int* cu_tokens, const int* slots, float* o, int T, int B, int H, int Dk, int Dv,
                       cudaStream_t stream);
-// the same for prompts, chunk by chunk in three launches (keys and values in multiples of 4 that fit the shared memory: the chunk's
+// the same for prompts, chunk by chunk in three launches behind one that turns the queries and keys of `proj` in place (keys and values in multiples of 4 that fit the shared memory: the chunk's
 // tokens, 64 / 32 / 16, or 0 where the sizes are not taken); n_chunks: sum over the step's sequences of ceil(tokens / chunk tokens)
 int vm_decayed_memory_chunk_tokens(int Dk, int Dv);
 long long vm_decayed_memory_scratch_floats(int T, int B, int H, int Dk, int Dv);
-int vm_decayed_memory_chunked(const float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* z_bias,
+int vm_decayed_memory_chunked(float* proj, int ld, int q_off, int k_off, int v_off, const float* z, int ldz, float tau, const float* z_bias,
                               const float* head_log_decay, const float* inv_freq, int rotary_dim, int pairing, float q_scale, float k_scale,
                               float* state, long long state_stride, int state_offset, const int* positions, const int* cu_tokens, const int* slots,
                               float* o, float* scratch, int n_chunks, int T, int B, int H, int Dk, int Dv, cudaStream_t stream);
