@@ -67,7 +67,7 @@ def test_without_streams_and_without_the_second_table():
     (lambda c: c["layers"][0]["mlp"]["router"]["groups"].update(count=4), "groups"),
     (lambda c: c["layers"][0]["mlp"].update(kind="sparse"), "kind"),
     (lambda c: c["embedding"]["bigram"].pop("buckets"), "buckets"),
-    (lambda c: c.update(streams=9), "streams"),
+    (lambda c: c.update(streams=17), "streams"),
     (lambda c: c.pop("norm"), "norm"),
     (lambda c: c.update(layers=[]), "layers"),
 ])

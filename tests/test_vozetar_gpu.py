@@ -199,7 +199,7 @@ def streams_config(hidden, streams, with_ff=True):
             "blocks": [block, copy.deepcopy(block)]}
 
 
-@pytest.mark.parametrize("streams,with_ff", [(1, True), (2, True), (3, True), (4, False), (8, True)])
+@pytest.mark.parametrize("streams,with_ff", [(1, True), (2, True), (3, True), (4, False), (8, True), (11, True)])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_copies_of_the_stream_are_read_mixed_and_summed(streams, with_ff, dtype, toy_plugin, tmp_path):
     """Two layers, so that a layer's last write is carried out by the next layer and the last one's by the model; mixing numbers of

@@ -6,7 +6,8 @@
 // Both steps are float32.  One kernel does a pending write (y given) and the next read (out given) of a token's row in one pass.
 #include "common.cuh"
 
-constexpr int HC_MAX_STREAMS = 8;
+constexpr int HC_MAX_STREAMS = 16;         // copies the plain kernel takes
+constexpr int HC_VEC_STREAMS = 8;          // ... and the kernel with 16-byte loads, which keeps a run of every copy in registers
 
 // One block per token.  y [T, hid] in the activation dtype or null; mix float32 [S, S] indexed [from, to]; w_out, w_in float32 [S];
 // out [T, hid] (activation dtype) = rmsnorm(u) * norm_w, or null.
@@ -91,7 +92,7 @@ streams_step_vec_kernel(float* __restrict__ h, long long stride, int S, const T*
                         const float* __restrict__ w_out, const float* __restrict__ w_in, const float* __restrict__ norm_w, float eps,
                         T* __restrict__ out, int hid) {
     __shared__ float red[32];
-    __shared__ float cm[HC_MAX_STREAMS * HC_MAX_STREAMS], co[HC_MAX_STREAMS], ci[HC_MAX_STREAMS];
+    __shared__ float cm[HC_VEC_STREAMS * HC_VEC_STREAMS], co[HC_VEC_STREAMS], ci[HC_VEC_STREAMS];
     if (threadIdx.x < S * S && y) cm[threadIdx.x] = mix[threadIdx.x];
     if (threadIdx.x < S) {
         if (y) co[threadIdx.x] = w_out[threadIdx.x];
@@ -108,19 +109,19 @@ streams_step_vec_kernel(float* __restrict__ h, long long stride, int S, const T*
         const int i = (threadIdx.x + c * HC_VEC_THREADS) * 4;
         u[c] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i >= hid) continue;
-        float4 x[HC_MAX_STREAMS];
+        float4 x[HC_VEC_STREAMS];
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+        for (int s = 0; s < HC_VEC_STREAMS; ++s)
             if (s < S) x[s] = *reinterpret_cast<const float4*>(h + s * stride + t * hid + i);
         if (y) {
             const float4 yv = hc_load4(y + t * hid + i);
-            float4 nx[HC_MAX_STREAMS];
+            float4 nx[HC_VEC_STREAMS];
 #pragma unroll
-            for (int to = 0; to < HC_MAX_STREAMS; ++to)
+            for (int to = 0; to < HC_VEC_STREAMS; ++to)
                 if (to < S) {
                     float4 a = make_float4(co[to] * yv.x, co[to] * yv.y, co[to] * yv.z, co[to] * yv.w);
 #pragma unroll
-                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+                    for (int s = 0; s < HC_VEC_STREAMS; ++s)
                         if (s < S) {
                             const float m = cm[s * S + to];
                             a.x = fmaf(m, x[s].x, a.x); a.y = fmaf(m, x[s].y, a.y); a.z = fmaf(m, x[s].z, a.z); a.w = fmaf(m, x[s].w, a.w);
@@ -128,7 +129,7 @@ streams_step_vec_kernel(float* __restrict__ h, long long stride, int S, const T*
                     nx[to] = a;
                 }
 #pragma unroll
-            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            for (int s = 0; s < HC_VEC_STREAMS; ++s)
                 if (s < S) {
                     x[s] = nx[s];
                     *reinterpret_cast<float4*>(h + s * stride + t * hid + i) = nx[s];
@@ -137,7 +138,7 @@ streams_step_vec_kernel(float* __restrict__ h, long long stride, int S, const T*
         if (out) {
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            for (int s = 0; s < HC_VEC_STREAMS; ++s)
                 if (s < S) { a.x = fmaf(ci[s], x[s].x, a.x); a.y = fmaf(ci[s], x[s].y, a.y); a.z = fmaf(ci[s], x[s].z, a.z); a.w = fmaf(ci[s], x[s].w, a.w); }
             u[c] = a;
             ss += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
@@ -161,7 +162,7 @@ VM_API int vm_streams_step(float* h, long long stride, int S, const void* y, con
     if (S < 1 || S > HC_MAX_STREAMS) return VM_ERR_UNSUPPORTED;
     if (hid <= 0 || (y && (!mix || !w_out)) || (out && (!w_in || !norm_w)) || (!y && !out)) return VM_ERR_BAD_ARG;
     if (act_dtype != VM_F32 && act_dtype != VM_BF16) return VM_ERR_UNSUPPORTED;
-    if (hid % 4 == 0 && hid >= 128 && hid <= 4 * HC_VEC_THREADS * HC_VEC_RUNS && stride % 4 == 0) {
+    if (S <= HC_VEC_STREAMS && hid % 4 == 0 && hid >= 128 && hid <= 4 * HC_VEC_THREADS * HC_VEC_RUNS && stride % 4 == 0) {
         if (act_dtype == VM_F32)
             vm_launch_pdl(streams_step_vec_kernel<float>, dim3(T), dim3(HC_VEC_THREADS), 0, stream, h, stride, S, (const float*)y, mix, w_out, w_in, norm_w,
                           eps, (float*)out, hid);
@@ -172,7 +173,7 @@ VM_API int vm_streams_step(float* h, long long stride, int S, const void* y, con
     }
     const size_t smem = (size_t)hid * sizeof(float);
     if (smem > 48 * 1024) return VM_ERR_UNSUPPORTED;
-    const int threads = hid >= 1024 ? 256 : 128;
+    const int threads = (hid >= 1024 || S > 8) ? 256 : 128;      // (the block's first S * S threads stage the mixing matrix)
     if (act_dtype == VM_F32)
         vm_launch_pdl(streams_step_kernel<float>, dim3(T), dim3(threads), smem, stream, h, stride, S, (const float*)y, mix, w_out, w_in, norm_w, eps,
                       (float*)out, hid);

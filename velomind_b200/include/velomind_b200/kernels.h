@@ -264,7 +264,7 @@ int vm_tc_qkv_rope(const void* A, long long lda, const void* W, int M, int K, vo
 // ---- hyper.cu: several copies of the residual stream; an embedding with a table read by pairs of tokens
 // Copy s of the stream is [T, hid] float32 at h + s * stride.  y (activation dtype, or null): every copy becomes
 // sum_s mix[s, to] x_s + w_out[to] * y (mix float32 [S, S] indexed [from, to]).  out (activation dtype, or null) then gets
-// rmsnorm(sum_s w_in[s] x_s) * norm_w.  At most 8 copies.
+// rmsnorm(sum_s w_in[s] x_s) * norm_w.  At most 16 copies.
 int vm_streams_step(float* h, long long stride, int S, const void* y, const float* mix, const float* w_out, const float* w_in, const float* norm_w,
                     float eps, void* out, int T, int hid, int act_dtype, cudaStream_t stream);
 int vm_streams_sum_rows(float* h, long long stride, int S, const int* rows, int n_rows, int hid, cudaStream_t stream);   // copy 0 <- the sum, at `rows`

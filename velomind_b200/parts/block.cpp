@@ -185,7 +185,7 @@ class HyperConnections : public Arrangement {
 public:
     HyperConnections(const BlockParts& p, int hidden, int streams, std::string first, std::string second, bool feed_forward)
         : p_(p), hidden_(hidden), S_(streams), first_(std::move(first)), second_(std::move(second)), feed_forward_(feed_forward) {
-        if (hidden <= 0 || streams < 1 || streams > 8) throw ConfigError(format("arrangement 'hyper_connections': streams (%d) must be within 1..8", streams));
+        if (hidden <= 0 || streams < 1 || streams > 16) throw ConfigError(format("arrangement 'hyper_connections': streams (%d) must be within 1..16", streams));
     }
     bool graph_safe() const override { return true; }
     bool mixes_streams() const override { return true; }
