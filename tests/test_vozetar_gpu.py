@@ -321,6 +321,29 @@ def test_keys_at_the_edges_of_window_and_kept_tokens_decide(form, window, keep, 
         run_cuts(engine, requests, plain, cuts, tol)
 
 
+def test_far_keys_decide_where_every_token_is_visible(toy_plugin, tmp_path):
+    """The attention without a window, with sharp scores: keys hundreds of tokens back carry much of the weight (checked on the plain
+    implementation: hiding everything beyond 128 tokens gives another answer at many places), across page borders, in prompts, pieces and
+    200 decode steps, with three taps whose kept rows cross every cut."""
+    import velomind_b200 as vm
+    m = C.attention(2, 1, 16, 16, 3.0, 3, base=100.0, dims=8)
+    w, folders = sharp_model(tmp_path, vm, "far", m, "full", 11)
+    requests = S.make_requests(64, (450, 130), seed=21)
+    plain = {}
+    for rid, toks in requests.items():
+        x = w["embed.weight"].astype(np.float64)[toks]
+        y = P.mixer_attention(x, P.sub(w, MIX), m, EPS)
+        plain[rid] = x + y
+        if len(toks) > 400:
+            near = P.mixer_attention(x, P.sub(w, MIX), dict(m, mask={"size": 128, "keep_first": 0}), EPS)
+            assert (np.abs(near - y).max(axis=1)[200:] > 0.05 * np.abs(y).max()).sum() >= 20
+    for dtype, tol in (("float32", 5e-5), ("bfloat16", 3e-2)):
+        engine = vm.Engine(vm.load_model(folders[dtype], dtype, "cuda:0"), 64 * 10, max_slots=2)
+        cuts = {"whole": S.steps_whole(requests), "tail": S.steps_tail_one_by_one(requests, tail=200),
+                "batches": S.steps_unequal_batches(requests, tails=(150, 60)), "pieces": steps_in_pieces(requests, (70, 2, 64, 1, 129))}
+        run_cuts(engine, requests, plain, cuts, tol)
+
+
 def test_a_sink_left_out_would_show(toy_plugin, tmp_path):
     import velomind_b200 as vm
     m = C.windowed(2, 2, 16, 16, 1.0, 40, 2, dims=8)
