@@ -338,7 +338,7 @@ def vozetar_config(z, x):
            "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": x["groups"], "keep": x["keep"]}}}
     dense = {"kind": "dense", "ff": z["ff"]}
     return {"architecture": "Vozetar", "vocab": z["vocab"], "width": z["width"], "streams": x["streams"], "norm": {"eps": 1e-6},
-            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 127, "mul_cur": 7}},
+            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 8191, "mul_cur": 31}},
             "layers": [{"type": "attention", "mixer": dict(att, conv=3), "mlp": dense}, {"type": "parallel", "mixer": par, "mlp": moe},
                        {"type": "parallel_2", "mixer": par2, "mlp": dense}, {"type": "parallel", "mixer": par, "mlp": moe}]}
 

@@ -62,11 +62,11 @@ VOZ_A = {
 # the stream; a window of exactly one page and one of 100; four taps; all experts of three; four groups of which one stays.
 VOZ_B = {
     "architecture": "Vozetar", "vocab": 320, "width": 256, "streams": 2, "norm": {"eps": 1e-6},
-    "embedding": {"bigram": {"buckets": 509, "mul_prev": 31, "mul_cur": 3}},
+    "embedding": {"bigram": {"buckets": 509, "mul_prev": 33, "mul_cur": 3}},
     "layers": [
         layer("parallel_2", {"left": windowed(4, 2, 64, 64, 0.12, 64, 4, base=1e6, dims=32, conv=4), "right": gated_memory(2, 32, 64, 16.0, 8)}, moe(8, 2, 64, 128, groups=(4, 1))),
-        layer("parallel", {"left": windowed(8, 2, 32, 32, 0.18, 100, 1, base=250000.0, dims=16), "left_scale": 1.2,
-                           "right": retention(4, 64, 32, (0.96875, 0.99, 0.998, 0.9995), base=1e6, dims=64), "right_scale": 0.5}, dense(384)),
+        layer("parallel", {"left": windowed(8, 2, 32, 32, 0.18, 100, 1, base=200000.0, dims=16), "left_scale": 1.1,
+                           "right": retention(4, 64, 32, (0.96875, 0.99, 0.998, 0.9995), base=1e6, dims=64), "right_scale": 0.6}, dense(384)),
         layer("attention", attention(4, 4, 64, 64, 0.125, 3), moe(3, 3, 128, 64)),
     ],
 }

@@ -69,6 +69,7 @@ json::Value rotation(const json::Value& mixer, long long dim, bool interleaved, 
     a.set("head_dim", dim);
     a.set("theta", rot.number("base"));
     a.set("rotary_dim", rot.integer_or("dims", dim));
+    a.set("exact_frequencies", 1);           // base^(-2i / dims) in double precision, rounded once
     return part(interleaved ? "rotary_interleaved" : "rotary_half_split", a);
 }
 

@@ -6,11 +6,13 @@ namespace vmb {
 
 // Rotary positions.  Frequencies as the reference builds them, in float32: inv_freq[j] = 1 / pow(theta, 2j / rotary_dim)
 // (examples/common/llama/llama_rope_mask.cpp:17-19); the angle pos * inv_freq[j] and its sine and cosine are computed in
-// float32 on the device.  Which two values of a head make pair j is the `pairing`: the reference's half-split
+// float32 on the device.  With `exact_frequencies` the frequencies are computed in double precision and rounded to float32 once.
+// Which two values of a head make pair j is the `pairing`: the reference's half-split
 // (j, j + rotary_dim/2) (src/cpu/ops/rotary_embedding.cpp:30-44), or interleaved (2j, 2j + 1).
 class Rotary : public Position {
 public:
-    Rotary(int head_dim, double theta, int rotary_dim, int pairing) : head_dim_(head_dim), rotary_dim_(rotary_dim), pairing_(pairing), theta_(theta) {
+    Rotary(int head_dim, double theta, int rotary_dim, int pairing, bool exact = false)
+        : head_dim_(head_dim), rotary_dim_(rotary_dim), pairing_(pairing), theta_(theta), exact_(exact) {
         if (rotary_dim_ % 2 || rotary_dim_ <= 0 || rotary_dim_ > head_dim_)
             throw ConfigError(format("rotary_dim %d must be even and within the head size %d", rotary_dim_, head_dim_));
     }
@@ -18,6 +20,10 @@ public:
     std::vector<float> inv_freq_host() const {
         std::vector<float> f(static_cast<size_t>(rotary_dim_ / 2));
         for (int j = 0; j < rotary_dim_ / 2; ++j) {
+            if (exact_) {                    // theta^(-2j / rotary_dim) in double precision, rounded once
+                f[j] = static_cast<float>(std::pow(theta_, -2.0 * j / rotary_dim_));
+                continue;
+            }
             const float exponent = (2.0f * static_cast<float>(j)) / static_cast<float>(rotary_dim_);
             f[j] = 1.0f / powf(static_cast<float>(theta_), exponent);
         }
@@ -31,6 +37,7 @@ public:
 private:
     int head_dim_, rotary_dim_, pairing_;
     double theta_;
+    bool exact_;
     DeviceTensor table_;
 };
 
@@ -44,7 +51,8 @@ public:
 namespace {
 std::shared_ptr<Part> make_rotary(const json::Value& a, int pairing, const char* kind) {
     const int head_dim = static_cast<int>(arg_int(a, "head_dim", kind));
-    return std::make_shared<Rotary>(head_dim, arg_number(a, "theta", kind), static_cast<int>(arg_int_or(a, "rotary_dim", head_dim, kind)), pairing);
+    return std::make_shared<Rotary>(head_dim, arg_number(a, "theta", kind), static_cast<int>(arg_int_or(a, "rotary_dim", head_dim, kind)), pairing,
+                                    arg_int_or(a, "exact_frequencies", 0, kind) != 0);
 }
 RegisterPart reg_half("position", "rotary_half_split", [](const json::Value& a) { return make_rotary(a, VM_PAIR_HALF_SPLIT, "rotary_half_split"); });
 RegisterPart reg_inter("position", "rotary_interleaved", [](const json::Value& a) { return make_rotary(a, VM_PAIR_INTERLEAVED, "rotary_interleaved"); });
